@@ -1,0 +1,568 @@
+// Device kernels of libfst_b200.so (sm_100a): shard gather/pack and realign.
+//
+// Both are pure byte movers bound by HBM bandwidth: every payload byte is read once and
+// written once (algorithmic traffic = 2 x payload).  The design rules are the ones that matter
+// for such a kernel on B200: 16-byte global loads and stores that a warp issues as whole
+// 512-byte rows (fully coalesced sectors on both sides), eight independent 16-byte loads in
+// flight per lane before the first store, streaming cache hints (the data is touched once),
+// and a grid of (SM count x resident CTAs per SM) that strides over the work.
+//
+// Work decomposition (gather).  An op is a strided 2-D byte copy (fst_copy2d_t).  Each row of
+// an op is cut into "subs" of at most SUB_BYTES; a sub is copied by one warp.  Sub boundaries
+// are placed so that, when the destination pitch allows it, every sub except the first of a
+// row starts on a 16-byte destination boundary.  Subs of all ops are numbered consecutively;
+// a warp finds the op of a sub by binary search over the ops' first-sub prefix.
+//
+// Alignment.  A sub is copied as: up to 15 head bytes (until the destination is 16-byte
+// aligned), a body of 16-byte destination vectors, up to 15 tail bytes.  If the source is
+// congruent to the destination modulo 16 the body is a plain vector copy; if not, each
+// destination vector is assembled from the two aligned 16-byte source words that straddle it
+// with funnel shifts.  The aligned words read may extend up to 15 bytes before or after the
+// source range, but always inside a 16-byte word that holds at least one byte of the range, so
+// they never touch another page.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "fst_internal.h"
+
+namespace fst {
+
+constexpr int SUB_BYTES = 2048;          // bytes one warp moves per sub (32 lanes x 4 x 16 B)
+constexpr int VEC_PER_LANE = SUB_BYTES / (32 * 16);
+constexpr int WARPS_PER_CTA = 8;
+constexpr int CTA_THREADS = WARPS_PER_CTA * 32;
+constexpr int SUBS_PER_WARP_STEP = 2;    // subs a warp loads before it starts storing
+
+// Device-side record of one op (64 bytes).
+struct GatherOp {
+    uint64_t src;
+    uint64_t dst;
+    uint64_t src_pitch;
+    uint64_t dst_pitch;
+    uint64_t row_bytes;
+    uint32_t subs_per_row;
+    uint32_t lead;       // (dst & 15) when every row has the same destination alignment, else 0
+    uint64_t first_sub;  // number of subs in all earlier ops
+    uint64_t n_subs;     // rows * subs_per_row
+};
+static_assert(sizeof(GatherOp) == 64, "GatherOp must stay 64 bytes");
+
+struct InlineOps {
+    GatherOp op[FST_GATHER_INLINE_OPS];
+};
+
+__device__ __forceinline__ uint4 ld_stream(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ uint4 ld_keep(const uint4 *p) {
+    // neighbouring lanes re-read this word in the shifted path: let it live in L1
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void st_stream(uint4 *p, const uint4 &v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+// Bytes [shift, shift+16) of the 32-byte pair (lo, hi); shift in 1..15.
+__device__ __forceinline__ uint4 funnel16(const uint4 &lo, const uint4 &hi, unsigned shift) {
+    const unsigned bits = (shift & 3u) * 8u;
+    uint4 r;
+    switch (shift >> 2) {
+        case 0:
+            r.x = __funnelshift_r(lo.x, lo.y, bits);
+            r.y = __funnelshift_r(lo.y, lo.z, bits);
+            r.z = __funnelshift_r(lo.z, lo.w, bits);
+            r.w = __funnelshift_r(lo.w, hi.x, bits);
+            break;
+        case 1:
+            r.x = __funnelshift_r(lo.y, lo.z, bits);
+            r.y = __funnelshift_r(lo.z, lo.w, bits);
+            r.z = __funnelshift_r(lo.w, hi.x, bits);
+            r.w = __funnelshift_r(hi.x, hi.y, bits);
+            break;
+        case 2:
+            r.x = __funnelshift_r(lo.z, lo.w, bits);
+            r.y = __funnelshift_r(lo.w, hi.x, bits);
+            r.z = __funnelshift_r(hi.x, hi.y, bits);
+            r.w = __funnelshift_r(hi.y, hi.z, bits);
+            break;
+        default:
+            r.x = __funnelshift_r(lo.w, hi.x, bits);
+            r.y = __funnelshift_r(hi.x, hi.y, bits);
+            r.z = __funnelshift_r(hi.y, hi.z, bits);
+            r.w = __funnelshift_r(hi.z, hi.w, bits);
+            break;
+    }
+    return r;
+}
+
+// One sub as seen by a warp after head/tail splitting.
+struct Span {
+    const unsigned char *src;  // first body byte (destination-aligned position)
+    unsigned char *dst;        // 16-byte aligned
+    unsigned nvec;             // body vectors (<= SUB_BYTES/16)
+    unsigned shift;            // src & 15
+};
+
+// Copies the head and tail bytes of [dst, dst+n) <- [src, src+n) and returns the body.
+__device__ __forceinline__ Span split_span(unsigned char *dst, const unsigned char *src,
+                                           unsigned n, unsigned lane) {
+    unsigned head = (16u - (unsigned)((uintptr_t)dst & 15u)) & 15u;
+    if (head > n) head = n;
+    if (lane < head) dst[lane] = src[lane];
+    dst += head;
+    src += head;
+    n -= head;
+    const unsigned nvec = n >> 4;
+    const unsigned tail = n & 15u;
+    if (lane < tail) dst[(nvec << 4) + lane] = src[(nvec << 4) + lane];
+    Span s;
+    s.src = src;
+    s.dst = dst;
+    s.nvec = nvec;
+    s.shift = (unsigned)((uintptr_t)src & 15u);
+    return s;
+}
+
+__device__ __forceinline__ void load_span(const Span &s, unsigned lane, uint4 (&v)[VEC_PER_LANE]) {
+    if (s.shift == 0) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(s.src);
+#pragma unroll
+        for (int j = 0; j < VEC_PER_LANE; ++j) {
+            const unsigned i = lane + 32u * j;
+            if (i < s.nvec) v[j] = ld_stream(p + i);
+        }
+    } else {
+        const uint4 *p = reinterpret_cast<const uint4 *>(s.src - s.shift);
+#pragma unroll
+        for (int j = 0; j < VEC_PER_LANE; ++j) {
+            const unsigned i = lane + 32u * j;
+            if (i < s.nvec) {
+                const uint4 lo = ld_keep(p + i);
+                const uint4 hi = ld_keep(p + i + 1);
+                v[j] = funnel16(lo, hi, s.shift);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void store_span(const Span &s, unsigned lane,
+                                           const uint4 (&v)[VEC_PER_LANE]) {
+    uint4 *p = reinterpret_cast<uint4 *>(s.dst);
+#pragma unroll
+    for (int j = 0; j < VEC_PER_LANE; ++j) {
+        const unsigned i = lane + 32u * j;
+        if (i < s.nvec) st_stream(p + i, v[j]);
+    }
+}
+
+// Index of the op that holds global sub g (ops sorted by first_sub, op[0].first_sub == 0).
+__device__ __forceinline__ unsigned find_op(const GatherOp *ops, unsigned n_ops, uint64_t g) {
+    unsigned lo = 0, hi = n_ops;  // invariant: ops[lo].first_sub <= g < ops[hi].first_sub
+    while (hi - lo > 1) {
+        const unsigned mid = (lo + hi) >> 1;
+        if (ops[mid].first_sub <= g) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ Span open_sub(const GatherOp *ops, unsigned n_ops, uint64_t g,
+                                         unsigned lane) {
+    const GatherOp &op = ops[find_op(ops, n_ops, g)];
+    const uint64_t local = g - op.first_sub;
+    const uint64_t row = local / op.subs_per_row;
+    const unsigned k = (unsigned)(local - row * op.subs_per_row);
+    // sub k of a row covers row bytes [k*SUB - lead, (k+1)*SUB - lead) clipped to the row
+    uint64_t beg = (uint64_t)k * SUB_BYTES;
+    beg = beg > op.lead ? beg - op.lead : 0;
+    uint64_t end = (uint64_t)(k + 1) * SUB_BYTES - op.lead;
+    if (end > op.row_bytes) end = op.row_bytes;
+    unsigned char *d = reinterpret_cast<unsigned char *>(op.dst + row * op.dst_pitch + beg);
+    const unsigned char *s =
+        reinterpret_cast<const unsigned char *>(op.src + row * op.src_pitch + beg);
+    return split_span(d, s, (unsigned)(end - beg), lane);
+}
+
+template <bool INLINE>
+__global__ void __launch_bounds__(CTA_THREADS)
+fst_gather_kernel(const __grid_constant__ InlineOps inline_ops, const GatherOp *__restrict__ table,
+                  unsigned n_ops, uint64_t total_subs) {
+    const GatherOp *ops = INLINE ? inline_ops.op : table;
+    const unsigned lane = threadIdx.x & 31u;
+    const uint64_t warp = (uint64_t)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
+    const uint64_t step = (uint64_t)gridDim.x * WARPS_PER_CTA * SUBS_PER_WARP_STEP;
+    for (uint64_t g = warp * SUBS_PER_WARP_STEP; g < total_subs; g += step) {
+        Span s[SUBS_PER_WARP_STEP];
+        uint4 v[SUBS_PER_WARP_STEP][VEC_PER_LANE];
+#pragma unroll
+        for (int u = 0; u < SUBS_PER_WARP_STEP; ++u) {
+            if (g + u < total_subs) {
+                s[u] = open_sub(ops, n_ops, g + u, lane);
+                load_span(s[u], lane, v[u]);
+            } else {
+                s[u].nvec = 0;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < SUBS_PER_WARP_STEP; ++u) store_span(s[u], lane, v[u]);
+    }
+}
+
+// Realign: one span, flat indexing, no op table.  dst + head is 16-byte aligned; the body has
+// nvec vectors read at byte offset `shift` inside aligned source words.
+constexpr int REALIGN_UNROLL = 4;
+__global__ void __launch_bounds__(CTA_THREADS)
+fst_realign_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
+                   uint64_t nbytes) {
+    unsigned head = (16u - (unsigned)((uintptr_t)dst & 15u)) & 15u;
+    if (head > nbytes) head = (unsigned)nbytes;
+    const uint64_t body = nbytes - head;
+    const uint64_t nvec = body >> 4;
+    const unsigned tail = (unsigned)(body & 15u);
+    if (blockIdx.x == 0) {
+        if (threadIdx.x < head) dst[threadIdx.x] = src[threadIdx.x];
+        if (threadIdx.x >= 32 && threadIdx.x - 32 < tail) {
+            const uint64_t o = head + (nvec << 4) + (threadIdx.x - 32);
+            dst[o] = src[o];
+        }
+    }
+    const unsigned char *sb = src + head;
+    uint4 *d = reinterpret_cast<uint4 *>(dst + head);
+    const unsigned shift = (unsigned)((uintptr_t)sb & 15u);
+    const uint4 *s = reinterpret_cast<const uint4 *>(sb - shift);
+    // a CTA moves REALIGN_UNROLL consecutive 4 KiB stripes per step (one vector per thread each)
+    const uint64_t stride = (uint64_t)gridDim.x * CTA_THREADS * REALIGN_UNROLL;
+    for (uint64_t base = (uint64_t)blockIdx.x * CTA_THREADS * REALIGN_UNROLL + threadIdx.x;
+         base < nvec; base += stride) {
+        uint4 v[REALIGN_UNROLL];
+        if (shift == 0) {
+#pragma unroll
+            for (int j = 0; j < REALIGN_UNROLL; ++j) {
+                const uint64_t i = base + (uint64_t)j * CTA_THREADS;
+                if (i < nvec) v[j] = ld_stream(s + i);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < REALIGN_UNROLL; ++j) {
+                const uint64_t i = base + (uint64_t)j * CTA_THREADS;
+                if (i < nvec) {
+                    const uint4 lo = ld_keep(s + i);
+                    const uint4 hi = ld_keep(s + i + 1);
+                    v[j] = funnel16(lo, hi, shift);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < REALIGN_UNROLL; ++j) {
+            const uint64_t i = base + (uint64_t)j * CTA_THREADS;
+            if (i < nvec) st_stream(d + i, v[j]);
+        }
+    }
+}
+
+}  // namespace fst
+
+// ------------------------------------------------------------------------------------------
+// Host side: argument checks, op table construction, workspaces, launches
+// ------------------------------------------------------------------------------------------
+namespace fst {
+
+namespace {
+
+constexpr unsigned TABLE_SLOT_OPS = 16384;  // ops per workspace slot (1 MiB of GatherOp)
+constexpr int TABLE_SLOTS = 4;
+constexpr int MAX_DEVICES = 64;
+
+// Per-device workspace of the table path: a small ring of (pinned host, device) op tables.  A
+// slot is reused only after the event recorded behind the launch that read it has completed.
+struct Workspace {
+    bool ready = false;
+    GatherOp *host_tab[TABLE_SLOTS] = {};
+    GatherOp *dev_tab[TABLE_SLOTS] = {};
+    cudaEvent_t done[TABLE_SLOTS] = {};
+    int next = 0;
+    int grid_limit = 0;
+};
+std::mutex g_ws_mutex;
+Workspace g_ws[MAX_DEVICES];
+int g_grid_limit[MAX_DEVICES];  // 0 = not computed yet
+
+int grid_limit_for(int dev) {
+    if (g_grid_limit[dev] == 0) {
+        int sms = 0, per_sm = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fst_gather_kernel<false>,
+                                                      CTA_THREADS, 0);
+        if (sms <= 0) sms = 148;
+        if (per_sm <= 0) per_sm = 4;
+        g_grid_limit[dev] = sms * per_sm;
+    }
+    return g_grid_limit[dev];
+}
+
+int ensure_workspace(int dev) {
+    Workspace &w = g_ws[dev];
+    if (w.ready) return FST_OK;
+    for (int i = 0; i < TABLE_SLOTS; ++i) {
+        cudaError_t e = cudaHostAlloc((void **)&w.host_tab[i], TABLE_SLOT_OPS * sizeof(GatherOp), 0);
+        if (e == cudaSuccess) e = cudaMalloc((void **)&w.dev_tab[i], TABLE_SLOT_OPS * sizeof(GatherOp));
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&w.done[i], cudaEventDisableTiming);
+        if (e != cudaSuccess) {
+            set_error("fst_gather: workspace allocation failed: %s", cudaGetErrorString(e));
+            return FST_ENOMEM;
+        }
+    }
+    w.ready = true;
+    return FST_OK;
+}
+
+// Turns caller ops into device records; returns total subs.  Contiguous ops collapse to one row.
+uint64_t build_ops(const fst_copy2d_t *in, uint64_t n, std::vector<GatherOp> &out,
+                   uint64_t &payload) {
+    uint64_t subs = 0;
+    payload = 0;
+    out.clear();
+    out.reserve(n);
+    for (uint64_t i = 0; i < n; ++i) {
+        fst_copy2d_t c = in[i];
+        if (c.rows == 0 || c.row_bytes == 0) continue;
+        if (c.rows > 1 && c.src_pitch == c.row_bytes && c.dst_pitch == c.row_bytes) {
+            c.row_bytes *= c.rows;
+            c.rows = 1;
+        }
+        GatherOp g;
+        g.src = c.src;
+        g.dst = c.dst;
+        g.src_pitch = c.rows > 1 ? c.src_pitch : 0;
+        g.dst_pitch = c.rows > 1 ? c.dst_pitch : 0;
+        g.row_bytes = c.row_bytes;
+        g.lead = (g.dst_pitch % 16 == 0) ? (uint32_t)(c.dst & 15u) : 0u;
+        const uint64_t spr = (c.row_bytes + g.lead + SUB_BYTES - 1) / SUB_BYTES;
+        // a row longer than 2^32 subs (8 TiB) is split by the caller; not reachable in practice
+        g.subs_per_row = (uint32_t)spr;
+        g.first_sub = subs;
+        g.n_subs = c.rows * spr;
+        subs += g.n_subs;
+        payload += c.rows * c.row_bytes;
+        out.push_back(g);
+    }
+    return subs;
+}
+
+int check_ops(const fst_copy2d_t *ops, uint64_t n, uint64_t src_base, uint64_t src_len,
+              uint64_t dst_base, uint64_t dst_len) {
+    for (uint64_t i = 0; i < n; ++i) {
+        const fst_copy2d_t &c = ops[i];
+        if (c.rows == 0 || c.row_bytes == 0) continue;
+        if (c.src == 0 || c.dst == 0) {
+            set_error("fst_gather: op %llu has a null address", (unsigned long long)i);
+            return FST_EINVAL;
+        }
+        if (c.rows > 1 && (c.src_pitch < c.row_bytes || c.dst_pitch < c.row_bytes)) {
+            set_error("fst_gather: op %llu: pitch smaller than row_bytes (rows would overlap)",
+                      (unsigned long long)i);
+            return FST_EINVAL;
+        }
+        if ((c.row_bytes + 15 + SUB_BYTES - 1) / SUB_BYTES > 0xffffffffull) {
+            set_error("fst_gather: op %llu: row_bytes too large", (unsigned long long)i);
+            return FST_ELIMIT;
+        }
+        const uint64_t s_end = c.src + (c.rows - 1) * c.src_pitch + c.row_bytes;
+        const uint64_t d_end = c.dst + (c.rows - 1) * c.dst_pitch + c.row_bytes;
+        if (src_len && (c.src < src_base || s_end > src_base + src_len)) {
+            set_error("fst_gather: op %llu reads [%#llx,%#llx) outside the source buffer "
+                      "[%#llx,%#llx)", (unsigned long long)i, (unsigned long long)c.src,
+                      (unsigned long long)s_end, (unsigned long long)src_base,
+                      (unsigned long long)(src_base + src_len));
+            return FST_ERANGE;
+        }
+        if (dst_len && (c.dst < dst_base || d_end > dst_base + dst_len)) {
+            set_error("fst_gather: op %llu writes [%#llx,%#llx) outside the destination buffer "
+                      "[%#llx,%#llx)", (unsigned long long)i, (unsigned long long)c.dst,
+                      (unsigned long long)d_end, (unsigned long long)dst_base,
+                      (unsigned long long)(dst_base + dst_len));
+            return FST_ERANGE;
+        }
+    }
+    return FST_OK;
+}
+
+unsigned grid_for(uint64_t total_subs, int limit) {
+    const uint64_t per_cta = (uint64_t)WARPS_PER_CTA * SUBS_PER_WARP_STEP;
+    uint64_t want = (total_subs + per_cta - 1) / per_cta;
+    if (want > (uint64_t)limit) want = (uint64_t)limit;
+    if (want == 0) want = 1;
+    return (unsigned)want;
+}
+
+}  // namespace
+
+int launch_realign(void *dst, const void *src, uint64_t nbytes, void *stream) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int limit = grid_limit_for(dev < MAX_DEVICES ? dev : 0);
+    const uint64_t per_cta = (uint64_t)CTA_THREADS * REALIGN_UNROLL * 16;
+    uint64_t want = (nbytes + per_cta - 1) / per_cta;
+    if (want > (uint64_t)limit) want = (uint64_t)limit;
+    if (want == 0) want = 1;
+    fst_realign_kernel<<<(unsigned)want, CTA_THREADS, 0, (cudaStream_t)stream>>>(
+        (unsigned char *)dst, (const unsigned char *)src, nbytes);
+    g_counters.kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    g_counters.bytes_realigned.fetch_add(nbytes, std::memory_order_relaxed);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace fst
+
+extern "C" int fst_realign(uint64_t dst, uint64_t src, uint64_t nbytes, uint64_t stream) {
+    using namespace fst;
+    clear_error();
+    if (!cuda_usable()) {
+        set_error("fst_realign: no CUDA device");
+        return FST_ENOCUDA;
+    }
+    if (nbytes == 0) return FST_OK;
+    if (dst == 0 || src == 0) {
+        set_error("fst_realign: null address");
+        return FST_EINVAL;
+    }
+    if (dst < src + nbytes && src < dst + nbytes) {
+        set_error("fst_realign: source and destination ranges overlap");
+        return FST_EINVAL;
+    }
+    const int e = launch_realign((void *)dst, (const void *)src, nbytes, (void *)stream);
+    if (e != 0) {
+        set_error("fst_realign: launch failed: %s", cudaGetErrorString((cudaError_t)e));
+        return FST_ECUDA;
+    }
+    return FST_OK;
+}
+
+extern "C" int fst_gather(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_base,
+                          uint64_t src_len, uint64_t dst_base, uint64_t dst_len,
+                          uint64_t stream) {
+    using namespace fst;
+    clear_error();
+    if (!cuda_usable()) {
+        set_error("fst_gather: no CUDA device");
+        return FST_ENOCUDA;
+    }
+    if (n_ops == 0) return FST_OK;
+    if (ops == nullptr) {
+        set_error("fst_gather: ops is null");
+        return FST_EINVAL;
+    }
+    int rc = check_ops(ops, n_ops, src_base, src_len, dst_base, dst_len);
+    if (rc != FST_OK) return rc;
+
+    std::vector<GatherOp> recs;
+    uint64_t payload = 0;
+    build_ops(ops, n_ops, recs, payload);
+    if (recs.empty()) return FST_OK;
+
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= MAX_DEVICES) {
+        set_error("fst_gather: device index %d not supported", dev);
+        return FST_ELIMIT;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    const int limit = grid_limit_for(dev);
+
+    size_t pos = 0;
+    while (pos < recs.size()) {
+        const size_t left = recs.size() - pos;
+        if (left <= FST_GATHER_INLINE_OPS) {
+            InlineOps p;
+            std::memset(&p, 0, sizeof(p));
+            const uint64_t base = recs[pos].first_sub;
+            uint64_t subs = 0;
+            for (size_t i = 0; i < left; ++i) {
+                p.op[i] = recs[pos + i];
+                p.op[i].first_sub -= base;
+                subs += p.op[i].n_subs;
+            }
+            fst_gather_kernel<true><<<grid_for(subs, limit), CTA_THREADS, 0, st>>>(
+                p, nullptr, (unsigned)left, subs);
+            pos += left;
+        } else {
+            rc = ensure_workspace(dev);
+            if (rc != FST_OK) return rc;
+            Workspace &w = g_ws[dev];
+            const int slot = w.next;
+            w.next = (w.next + 1) % TABLE_SLOTS;
+            cudaError_t e = cudaEventSynchronize(w.done[slot]);
+            if (e != cudaSuccess) {
+                set_error("fst_gather: waiting for a workspace slot failed: %s",
+                          cudaGetErrorString(e));
+                return FST_ECUDA;
+            }
+            const size_t take = std::min<size_t>(left, TABLE_SLOT_OPS);
+            const uint64_t base = recs[pos].first_sub;
+            uint64_t subs = 0;
+            for (size_t i = 0; i < take; ++i) {
+                w.host_tab[slot][i] = recs[pos + i];
+                w.host_tab[slot][i].first_sub -= base;
+                subs += recs[pos + i].n_subs;
+            }
+            e = cudaMemcpyAsync(w.dev_tab[slot], w.host_tab[slot], take * sizeof(GatherOp),
+                                cudaMemcpyHostToDevice, st);
+            if (e != cudaSuccess) {
+                set_error("fst_gather: op table upload failed: %s", cudaGetErrorString(e));
+                return FST_ECUDA;
+            }
+            InlineOps none;
+            std::memset(&none, 0, sizeof(none));
+            fst_gather_kernel<false><<<grid_for(subs, limit), CTA_THREADS, 0, st>>>(
+                none, w.dev_tab[slot], (unsigned)take, subs);
+            cudaEventRecord(w.done[slot], st);
+            pos += take;
+        }
+        g_counters.kernel_launches.fetch_add(1, std::memory_order_relaxed);
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            set_error("fst_gather: launch failed: %s", cudaGetErrorString(e));
+            return FST_ECUDA;
+        }
+    }
+    g_counters.bytes_gathered.fetch_add(payload, std::memory_order_relaxed);
+    return FST_OK;
+}
+
+extern "C" int fst_release_workspaces(void) {
+    using namespace fst;
+    if (!cuda_usable()) return FST_OK;
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    int cur = 0;
+    cudaGetDevice(&cur);
+    for (int d = 0; d < MAX_DEVICES; ++d) {
+        Workspace &w = g_ws[d];
+        if (!w.ready) continue;
+        cudaSetDevice(d);
+        for (int i = 0; i < TABLE_SLOTS; ++i) {
+            cudaEventSynchronize(w.done[i]);
+            cudaEventDestroy(w.done[i]);
+            cudaFree(w.dev_tab[i]);
+            cudaFreeHost(w.host_tab[i]);
+        }
+        w = Workspace();
+    }
+    cudaSetDevice(cur);
+    return FST_OK;
+}

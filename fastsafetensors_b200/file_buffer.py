@@ -1,0 +1,139 @@
+"""``FilesBufferOnDevice``: name-addressed access to the tensors of a batch of loaded files.
+
+Public surface of upstream ``fastsafetensors/file_buffer.py``: ``get_tensor``, ``get_sharded``,
+``push_tensor``, ``get_multi_cols``, ``as_dict`` and their ``*_wrapped`` forms, ``get_filename``,
+``get_shape``, ``close``, and the attributes ``key_to_rank_lidx``, ``rank_loaders``,
+``auto_mem_delete`` that callers read.  In multi-rank use every rank must call these methods in
+the same order (they end in collectives).
+"""
+
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import Any, Dict, List, Optional, Set, Tuple
+
+from .common import init_logger
+from .frameworks import ProcessGroupBase, TensorBase
+from .st_types import Device, DType
+from .tensor_factory import LazyTensorFactory
+
+logger = init_logger(__name__)
+
+
+class FilesBufferOnDevice:
+    def __init__(self, rank_loaders: Dict[int, List[LazyTensorFactory]], pg: ProcessGroupBase,
+                 framework, auto_mem_delete: bool = True):
+        self.framework = framework
+        self.rank_loaders = rank_loaders
+        self.pg = pg
+        self.key_to_rank_lidx: Dict[str, Tuple[int, int]] = {}
+        # per file: names already handed out; a file image is dropped once all were
+        self.instantiated: Dict[int, Dict[int, Dict[str, bool]]] = {}
+        for rank, loaders in rank_loaders.items():
+            self.instantiated[rank] = {}
+            for lidx, loader in enumerate(loaders):
+                self.instantiated[rank][lidx] = {}
+                for key in loader.metadata.tensors:
+                    if key in self.key_to_rank_lidx:
+                        raise Exception(f"FilesBufferOnDevice: key {key} must be unique among files")
+                    self.key_to_rank_lidx[key] = (rank, lidx)
+        # with one rank results alias the images, so the images must stay
+        self.auto_mem_delete = auto_mem_delete and pg.size() > 1
+
+    def close(self) -> None:
+        """Drop the file images.  Tensors obtained with one rank are views of them."""
+        for loaders in self.rank_loaders.values():
+            for loader in loaders:
+                loader.free_dev_ptrs()
+        self.rank_loaders = {}
+
+    def get_filename(self, tensor_name: str) -> str:
+        if tensor_name not in self.key_to_rank_lidx:
+            return ""
+        rank, lidx = self.key_to_rank_lidx[tensor_name]
+        return self.rank_loaders[rank][lidx].metadata.src
+
+    def get_shape(self, tensor_name: str) -> List[int]:
+        rank, lidx = self._get_rank_lidx(tensor_name)
+        return self.rank_loaders[rank][lidx].metadata.tensors[tensor_name].shape
+
+    def _get_rank_lidx(self, tensor_name: str) -> Tuple[int, int]:
+        try:
+            return self.key_to_rank_lidx[tensor_name]
+        except KeyError:
+            raise ValueError(f"_get_rank: key {tensor_name} was not found in files") from None
+
+    def _mark(self, rank: int, lidx: int, tensor_name: str) -> None:
+        """Record that ``tensor_name`` was handed out; free its file image after the last one."""
+        if not self.auto_mem_delete:
+            return
+        loader = self.rank_loaders[rank][lidx]
+        seen = self.instantiated[rank][lidx]
+        seen[tensor_name] = True
+        if len(seen) == len(loader.metadata.tensors):
+            if self.pg.rank() == rank:
+                logger.debug("free_dev_ptrs: lidx=%d, src=%s", lidx, loader.metadata.src)
+            loader.free_dev_ptrs()
+
+    def _get_tensor(self, rank: int, lidx: int, tensor_name: str, ret: TensorBase,
+                    device: Optional[Device], dtype: DType) -> TensorBase:
+        self._mark(rank, lidx, tensor_name)
+        return ret.to(device=device, dtype=dtype)
+
+    # ------------------------------------------------------------------ one tensor
+    def get_sharded_wrapped(self, tensor_name: str, dim: int, device: Optional[Device] = None,
+                            dtype: DType = DType.AUTO) -> TensorBase:
+        rank, lidx = self._get_rank_lidx(tensor_name)
+        t = self.rank_loaders[rank][lidx].shuffle(self.pg, tensor_name, dim)
+        return self._get_tensor(rank, lidx, tensor_name, t, device, dtype)
+
+    def get_sharded(self, tensor_name: str, dim: int, device: Optional[Device] = None,
+                    dtype: DType = DType.AUTO) -> Any:
+        """This rank's block of ``tensor_name`` on ``dim`` (``dim == -1``: the whole tensor)."""
+        return self.get_sharded_wrapped(tensor_name, dim, device, dtype).get_raw()
+
+    def get_tensor_wrapped(self, tensor_name: str, device: Optional[Device] = None,
+                           dtype: DType = DType.AUTO) -> TensorBase:
+        return self.get_sharded_wrapped(tensor_name, -1, device, dtype)
+
+    def get_tensor(self, tensor_name: str, device: Optional[Device] = None,
+                   dtype: DType = DType.AUTO) -> Any:
+        """The whole tensor on every rank (broadcast from the rank that read its file)."""
+        return self.get_tensor_wrapped(tensor_name, device, dtype).get_raw()
+
+    def push_tensor(self, tensor_name: str, dst_rank: int, device: Optional[Device] = None,
+                    dtype: DType = DType.AUTO) -> Optional[Any]:
+        """The whole tensor on ``dst_rank`` only; None elsewhere."""
+        rank, lidx = self._get_rank_lidx(tensor_name)
+        t = self.rank_loaders[rank][lidx].push(self.pg, tensor_name, dst_rank, rank)
+        if t is None:
+            self._mark(rank, lidx, tensor_name)
+            return None
+        return self._get_tensor(rank, lidx, tensor_name, t, device, dtype).get_raw()
+
+    # ------------------------------------------------------------------ column groups
+    def get_multi_cols(self, tensor_names: List[str], dim: int, device: Optional[Device] = None,
+                       dtype: DType = DType.AUTO) -> TensorBase:
+        """This rank's shards of ``tensor_names`` concatenated on ``dim`` (a wrapped tensor, as
+        upstream returns).  Names are grouped by file; groups are emitted in (owner, file)
+        order, names inside a group in the order given (file_buffer.py:204-221)."""
+        groups: Dict[Tuple[int, int], List[str]] = {}
+        for name in tensor_names:
+            groups.setdefault(self._get_rank_lidx(name), []).append(name)
+        parts: List[TensorBase] = []
+        for (rank, lidx) in sorted(groups):
+            parts.append(self.rank_loaders[rank][lidx].shuffle_multi_cols(self.pg, groups[(rank, lidx)], dim))
+        ret = parts[0] if len(parts) == 1 else self.framework.concat_tensors(parts, dim=dim)
+        for name in tensor_names:
+            self._mark(*self.key_to_rank_lidx[name], name)
+        return ret.to(device=device, dtype=dtype)
+
+    # ------------------------------------------------------------------ many tensors
+    def as_dict(self, tensor_shard_dim: "OrderedDict[str, int]") -> Dict[str, TensorBase]:
+        """``{name: wrapped tensor}`` for ``{name: dim}`` (``-1`` = replicate)."""
+        out: Dict[str, TensorBase] = {}
+        for name, dim in tensor_shard_dim.items():
+            rank, lidx = self._get_rank_lidx(name)
+            out[name] = self.rank_loaders[rank][lidx].shuffle(self.pg, name, dim)
+            self._mark(rank, lidx, name)
+        return out

@@ -93,10 +93,11 @@ class TorchTensor(TensorBase):
 
 
 def _bytes_view(t: torch.Tensor) -> torch.Tensor:
-    """The tensor's storage as uint8 (collectives move bytes, whatever the dtype)."""
-    if t.dim() == 0:
-        t = t.reshape(1)
-    return t if t.dtype == torch.uint8 else t.view(torch.uint8)
+    """The tensor's bytes as a flat uint8 view (collectives move bytes, whatever the dtype)."""
+    if not t.is_contiguous():
+        raise ValueError("collectives need contiguous tensors")
+    flat = t.reshape(-1)
+    return flat if flat.dtype == torch.uint8 else flat.view(torch.uint8)
 
 
 @dataclass

@@ -133,7 +133,12 @@ class BaseSafeTensorsFileLoader:
             for factory in mine:
                 factory.free_dev_ptrs()
             raise error
-        return FilesBufferOnDevice(factories, pg=self.pg, framework=self.framework)
+        try:
+            return FilesBufferOnDevice(factories, pg=self.pg, framework=self.framework)
+        except Exception:
+            for factory in mine:
+                factory.free_dev_ptrs()
+            raise
 
 
 class SafeTensorsFileLoader(BaseSafeTensorsFileLoader):

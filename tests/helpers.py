@@ -1,0 +1,28 @@
+"""Helpers shared by the parity tests."""
+
+import hashlib
+from typing import List
+
+import numpy as np
+import torch
+
+
+def digest_tensor(t) -> str:
+    t = t.get_raw() if hasattr(t, "get_raw") else t
+    raw = t.detach().contiguous().reshape(-1).view(torch.uint8).cpu().numpy().tobytes()
+    return hashlib.sha256(raw).hexdigest()[:16]
+
+
+def record(t) -> List:
+    """[shape, dtype, digest] in the form tests/golden/reference_outputs.json stores."""
+    t = t.get_raw() if hasattr(t, "get_raw") else t
+    return [list(t.shape), str(t.dtype).replace("torch.", ""), digest_tensor(t)]
+
+
+def digest_bytes(raw: np.ndarray) -> str:
+    return hashlib.sha256(np.ascontiguousarray(raw).tobytes()).hexdigest()[:16]
+
+
+def tensor_bytes(t) -> np.ndarray:
+    t = t.get_raw() if hasattr(t, "get_raw") else t
+    return t.detach().contiguous().reshape(-1).view(torch.uint8).cpu().numpy()

@@ -1,0 +1,493 @@
+"""Benchmark of the safetensors -> HBM load path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload: the Llama-3-8B-shaped bf16 checkpoint (4 files, 16.06 GB of tensor data, synthetic
+values), loaded tensor-parallel.  With one GPU the single rank owns every file and packs the
+shards of all 8 tensor-parallel ranks (what the owner of a file does before the exchange); with N
+GPUs the files are owned round-robin, tensor parallelism is N-way and the shards are exchanged
+over NCCL.  One JSON line is printed by rank 0:
+
+* ``value``    GB/s of tensor data sharded per second with the file images already resident in
+               HBM (gather kernel + exchange), timed with CUDA events, max over ranks;
+* ``e2e``      the same checkpoint from files on disk to shards in HBM through the public loader
+               API, page cache dropped before every step (cold reads), wall clock between device
+               synchronisations; ``e2e_warm`` is the same with the files in the page cache;
+* ``roofline`` the gather kernel against the measured HBM copy bandwidth;
+* ``cpu_baseline`` upstream fastsafetensors (CPU, gloo ranks) on a bounded sample.
+
+``--impl reference`` runs upstream's own CPU path (built into ``oracle/_ref``) on the same files.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from collections import OrderedDict
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GB = 1e9
+WORKLOAD = "llama3-8b"
+L2_BYTES = 126 * (1 << 20)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    ap.add_argument("--config", default=WORKLOAD)
+    ap.add_argument("--scale", default="full", choices=("full", "tiny"))
+    ap.add_argument("--dir", default=os.environ.get("FST_BENCH_DIR", "/tmp/fst_bench"))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="only the device-resident phase (for profiler captures)")
+    return ap.parse_args()
+
+
+def dist_env():
+    return (int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)),
+            int(os.environ.get("WORLD_SIZE", 1)))
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [x for x in sm if x > 0.5 * max(mx or [1])] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------
+# workload
+# ------------------------------------------------------------------------------------------
+def plan_for(spec, tp: int) -> "OrderedDict[str, tuple]":
+    return OrderedDict((t.name, (t.action[0], t.action[1] % tp) if t.action[0] == "push" else t.action)
+                       for t in spec.tensors)
+
+
+def prepare_files(spec, directory: str, rank: int, barrier) -> list:
+    from fastsafetensors_b200 import synth
+
+    out = os.path.join(directory, f"{spec.name}")
+    if rank == 0:
+        t0 = time.time()
+        paths = synth.write_checkpoint(spec, out, fsync=True)
+        sys.stderr.write(f"[bench] checkpoint {spec.name}: {len(paths)} files, "
+                         f"{spec.data_bytes / GB:.2f} GB in {out} ({time.time() - t0:.1f} s)\n")
+    barrier()
+    groups = synth.partition(spec)
+    return sorted(os.path.join(out, synth.file_name(spec, k, len(groups))) for k in range(len(groups)))
+
+
+# ------------------------------------------------------------------------------------------
+# this repository's arm
+# ------------------------------------------------------------------------------------------
+def b200_arm(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    import fastsafetensors_b200 as fst
+    from fastsafetensors_b200 import _native as nat
+    from fastsafetensors_b200 import cpp, synth
+    from fastsafetensors_b200.batch import ShardExchange
+
+    rank, local_rank, world = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the b200 arm has no CPU substitute")
+    torch.cuda.set_device(local_rank)
+    device = f"cuda:{local_rank}"
+    pg = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(device))
+        pg = dist.group.WORLD
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    spec = synth.config(args.config, args.scale)
+    tp = spec.tp if world == 1 else world
+    plan = plan_for(spec, tp)
+    paths = prepare_files(spec, args.dir, rank, barrier)
+    owners = synth.owners(paths, world)
+    data_bytes = spec.data_bytes
+
+    def open_loader():
+        return fst.SafeTensorsFileLoader(pg if pg is not None else fst.SingleGroup(), torch.device(device),
+                                         nogds=True)
+
+    def make_exchange(fb) -> ShardExchange:
+        return ShardExchange(fb, plan, tp, rank if world > 1 else 0, local=(world == 1))
+
+    # ---------------------------------------------------------------- device-resident phase
+    loader = open_loader()
+    loader.add_filenames(owners)
+    fb = loader.copy_files_to_device()
+    ex = make_exchange(fb)
+    stream = torch.cuda.current_stream()
+    for _ in range(max(3, args.warmup)):
+        ex.run()
+    torch.cuda.synchronize()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    m0 = cpp.get_cpp_metrics()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kernel_events = []
+    torch.cuda.synchronize()
+    barrier()
+    start.record(stream)
+    for _ in range(args.steps):
+        # ex.run() with an event pair around every gather launch
+        for arr, n, base, length in ex.launches:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            nat.check(nat.lib.fst_gather(arr, n, 0, 0, base, length, stream.cuda_stream), "fst_gather")
+            b.record(stream)
+            kernel_events.append((a, b))
+        if world > 1:
+            lay = ex.layout
+            dist.all_to_all_single(ex.recv[:sum(lay.recv_sizes(rank))], ex.send, lay.recv_sizes(rank),
+                                   lay.send_sizes(rank), group=pg)
+    stop.record(stream)
+    torch.cuda.synchronize()
+    barrier()
+    m1 = cpp.get_cpp_metrics()
+    resident_ms = max_over_ranks(start.elapsed_time(stop)) / args.steps
+    kernel_ms_total = sum(a.elapsed_time(b) for a, b in kernel_events)
+    n_launch = len(kernel_events)
+    launches_timed = m1.kernel_launches - m0.kernel_launches
+    payload_per_step = ex.payload_bytes                      # bytes this rank's kernel moves
+    kernel_ms = kernel_ms_total / max(1, n_launch)           # average launch duration
+    alg_bytes_per_launch = 2.0 * payload_per_step * args.steps / max(1, n_launch)
+    achieved = alg_bytes_per_launch / (kernel_ms * 1e-3) / GB if kernel_ms > 0 else 0.0
+    clocks = sampler.stop() if sampler else None
+    # a light checksum of the result so the step has a device->host read
+    check = int(ex.recv[:: max(1, ex.recv.numel() // 4096)].to(torch.int64).sum().item())
+    del ex
+    fb.close()
+    loader.close()
+    torch.cuda.empty_cache()
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+
+    result = {
+        "metric": "safetensors->HBM tensor-parallel load throughput",
+        "value": round(data_bytes / (resident_ms * 1e-3) / GB, 2),
+        "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": round(resident_ms, 4),
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "u8",
+        "data": "synthetic",
+        "config": {
+            "workload": f"{spec.name} ({args.scale}): {len(spec.tensors)} tensors, {len(paths)} files, "
+                        f"{data_bytes} data bytes, tensor-parallel {tp}-way"
+                        + (" packed by one rank for all destinations" if world == 1 else
+                           " files owned round-robin, NCCL all-to-all"),
+            "value_phase": "file images resident in HBM -> gather kernel (+ exchange)",
+            "l2": f"inputs ({payload_per_step} B per rank and step) larger than L2 ({L2_BYTES} B), no flush",
+            "tp": tp,
+        },
+        "gpu_launches": int(launches_timed),
+        "roofline": {
+            "bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+            "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
+            "kernel": "fst_gather_kernel", "launches": n_launch,
+            "avg_launch_ms": round(kernel_ms, 4),
+            "algorithmic_bytes_per_launch": int(alg_bytes_per_launch),
+        },
+        "clocks": clocks,
+        "result_checksum": check,
+    }
+
+    # ---------------------------------------------------------------- end to end (public API)
+    def e2e_step():
+        torch.cuda.synchronize()
+        barrier()
+        t0 = time.perf_counter()
+        ld = open_loader()
+        ld.add_filenames(owners)
+        buf = ld.copy_files_to_device()
+        if world == 1:
+            got = buf.shard_locally(plan, tp)
+            probe = next(iter(got[-1].values())).get_raw()
+        else:
+            got = buf.exchange(plan)
+            probe = next(iter(got.values())).get_raw()
+        head = probe.reshape(-1)[:1024].cpu()      # device -> host read of the result
+        torch.cuda.synchronize()
+        barrier()
+        dt = time.perf_counter() - t0
+        del got, probe
+        buf.close()
+        ld.close()
+        return max_over_ranks(dt), int(head.numel() * head.element_size())
+
+    def e2e_phase(cold: bool, steps: int, warmup: int):
+        times, d2h = [], 0
+        for i in range(warmup + steps):
+            if cold:
+                if rank == 0:
+                    synth.drop_page_cache(paths)
+                barrier()
+            dt, d2h = e2e_step()
+            if i >= warmup:
+                times.append(dt)
+            torch.cuda.empty_cache()
+        mean = sum(times) / len(times)
+        return {"value": round(data_bytes / mean / GB, 3), "unit": "GB/s",
+                "h2d_bytes_per_step": int(data_bytes), "d2h_bytes_per_step": d2h,
+                "s_per_step": round(mean, 4), "steps": steps,
+                "page_cache": "dropped before every step" if cold else "warm"}
+
+    if not args.no_e2e and not args.kernel_only:
+        mA = cpp.get_cpp_metrics()
+        result["e2e"] = e2e_phase(True, args.steps, 1)
+        mB = cpp.get_cpp_metrics()
+        result["e2e"]["io"] = {"direct_requests": mB.direct_io_requests - mA.direct_io_requests,
+                               "buffered_requests": mB.buffered_io_requests - mA.buffered_io_requests}
+        result["e2e_warm"] = e2e_phase(False, min(args.steps, 3), 1)
+        result["storage_read"] = storage_roofline(paths, owners[rank], rank, barrier, max_over_ranks)
+        if result["storage_read"]["cold_direct_gbs"]:
+            result["e2e"]["frac_of_storage_read"] = round(
+                result["e2e"]["value"] / result["storage_read"]["cold_direct_gbs"], 3)
+    if rank == 0 and not args.no_cpu_baseline and not args.kernel_only:
+        result["cpu_baseline"] = cpu_baseline(spec, paths)
+    if world > 1:
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+def storage_roofline(paths, my_paths, rank, barrier, max_over_ranks) -> dict:
+    """Cold O_DIRECT read bandwidth of the same files with the same thread count, into host
+    memory (the role fio plays where it is installed): the ceiling for a cold end-to-end load."""
+    from fastsafetensors_b200 import _native as nat
+    from fastsafetensors_b200 import cpp, synth
+    import numpy as np
+
+    if rank == 0:
+        synth.drop_page_cache(paths)
+    barrier()
+    total = sum(os.path.getsize(p) for p in paths)
+    scratch = np.empty(max([os.path.getsize(p) for p in my_paths] or [1]), dtype=np.uint8)
+    buf = cpp.gds_device_buffer(scratch.ctypes.data, scratch.size, False)
+    reader = cpp.Reader(-1, 16, 4 << 20, 2, io_mode=nat.IO_DIRECT)
+    barrier()
+    t0 = time.perf_counter()
+    for p in my_paths:
+        n = os.path.getsize(p) // 4096 * 4096
+        reader.wait(reader.submit(p, 0, n, buf, 0))
+    barrier()
+    dt = max_over_ranks(time.perf_counter() - t0)
+    reader.close()
+    return {"cold_direct_gbs": round(total / dt / GB, 3), "threads_per_rank": 16, "block": "4 MiB",
+            "tool": "native reader, O_DIRECT, host destination (fio is not installed)"}
+
+
+# ------------------------------------------------------------------------------------------
+# upstream's CPU path (the checker's build in oracle/_ref), timed on the host cores
+# ------------------------------------------------------------------------------------------
+REF_DIR = os.path.join(ROOT, "oracle", "_ref")
+
+
+def _reference_rank(rank: int, world: int, paths, plan_items, phases, port: int, out_path: str) -> None:
+    """One gloo rank running UPSTREAM's loader on device "cpu": files owned round-robin, every
+    tensor requested by the plan (get_sharded / get_tensor / push_tensor)."""
+    sys.path.insert(0, REF_DIR)
+    import torch
+    import torch.distributed as dist
+
+    import fastsafetensors as ref
+    from fastsafetensors_b200 import synth
+
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
+    pg = None
+    if world > 1:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        pg = dist.group.WORLD
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    owners = synth.owners(paths, world)
+    results = {}
+    for label, cold, steps, warmup in phases:
+        times = []
+        for i in range(warmup + steps):
+            if cold:
+                if rank == 0:
+                    synth.drop_page_cache(paths)
+            barrier()
+            t0 = time.perf_counter()
+            loader = ref.SafeTensorsFileLoader(pg if pg is not None else ref.SingleGroup(), "cpu", nogds=True)
+            loader.add_filenames(owners)
+            fb = loader.copy_files_to_device()
+            keep = []
+            for name, action in plan_items:
+                if action[0] == "shard":
+                    keep.append(fb.get_sharded(name, action[1]))
+                elif action[0] == "replicate":
+                    keep.append(fb.get_tensor(name))
+                else:
+                    keep.append(fb.push_tensor(name, action[1]))
+            barrier()
+            dt = time.perf_counter() - t0
+            del keep
+            fb.close()
+            loader.close()
+            if i >= warmup:
+                times.append(dt)
+        results[label] = times
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump(results, f)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(spec, paths, tp: int, phases) -> dict:
+    import tempfile
+
+    import torch.multiprocessing as mp
+
+    if not os.path.exists(os.path.join(REF_DIR, "fastsafetensors", "__init__.py")):
+        raise FileNotFoundError("oracle/_ref is missing (build it with oracle/build_ref.sh)")
+    plan_items = list(plan_for(spec, tp).items())
+    with tempfile.TemporaryDirectory() as tmp:
+        out_path = os.path.join(tmp, "times.json")
+        port = 29800 + os.getpid() % 100
+        if tp == 1:
+            _reference_rank(0, 1, paths, plan_items, phases, port, out_path)
+        else:
+            mp.spawn(_reference_rank, args=(tp, paths, plan_items, phases, port, out_path), nprocs=tp, join=True)
+        return json.load(open(out_path))
+
+
+def cpu_baseline(spec, paths) -> dict:
+    """Upstream on the host cores, one cold and one warm pass over the same checkpoint."""
+    tp = spec.tp
+    try:
+        t = run_reference(spec, paths, tp, [("cold", True, 1, 0), ("warm", False, 1, 0)])
+    except Exception as e:  # noqa: BLE001
+        return {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference",
+                "sample": f"failed: {type(e).__name__}: {e}"}
+    cold, warm = t["cold"][0], t["warm"][0]
+    return {"value": round(spec.data_bytes / cold / GB, 3), "unit": "GB/s", "cores": os.cpu_count(),
+            "kind": "reference",
+            "sample": f"upstream fastsafetensors 0.3.2, device cpu, nogds, {tp} gloo ranks, whole "
+                      f"{spec.name} checkpoint once with the page cache dropped ({cold:.2f} s) and "
+                      f"once warm ({warm:.2f} s), library defaults (16 threads, 16 MiB bounce, one "
+                      f"request per file)",
+            "warm_value": round(spec.data_bytes / warm / GB, 3)}
+
+
+def reference_arm(args) -> dict:
+    from fastsafetensors_b200 import synth
+
+    rank, _, world = dist_env()
+    if rank != 0:
+        return {}
+    spec = synth.config(args.config, args.scale)
+    tp = spec.tp if world == 1 else world
+    paths = prepare_files(spec, args.dir, 0, lambda: None)
+    phases = [("cold", True, args.steps, 1), ("warm", False, min(args.steps, 3), 1)]
+    t = run_reference(spec, paths, tp, phases)
+    cold = sum(t["cold"]) / len(t["cold"])
+    warm = sum(t["warm"]) / len(t["warm"])
+    v = round(spec.data_bytes / cold / GB, 3)
+    sample = (f"upstream fastsafetensors 0.3.2 (oracle/_ref), device cpu, nogds, {tp} gloo ranks on "
+              f"{os.cpu_count()} cores, whole {spec.name} checkpoint per step, page cache dropped "
+              f"before every step")
+    return {
+        "impl": "reference",
+        "metric": "safetensors->HBM tensor-parallel load throughput",
+        "value": v, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": 1,
+        "ms_per_step": round(cold * 1e3, 2), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": f"{spec.name} ({args.scale}): {len(spec.tensors)} tensors, {len(paths)} files, "
+                               f"{spec.data_bytes} data bytes, tensor-parallel {tp}-way, host memory", "tp": tp},
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference",
+                         "sample": sample},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "page_cache": "dropped before every step"},
+        "e2e_warm": {"value": round(spec.data_bytes / warm / GB, 3), "unit": "GB/s"},
+        "gpu_launches": 0,
+    }
+
+
+def main() -> None:
+    args = parse_args()
+    out = reference_arm(args) if args.impl == "reference" else b200_arm(args)
+    if out:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,225 @@
+"""Batched redistribution plan: many tensors, all destination ranks, one gather launch per file
+and one exchange per batch.
+
+Upstream moves one tensor per collective (``tensor_factory.py:143,186,258``: a broadcast or a
+scatter per tensor, each followed by a device-wide synchronisation).  With file ownership dealt
+round-robin the sum of those scatters is a balanced all-to-all: every owner keeps 1/W of what it
+read and ships (W-1)/W, every rank receives (W-1)/W of a file-equivalent.  This module lays that
+exchange out explicitly:
+
+* ``BatchLayout`` assigns every requested (tensor, destination rank) pair a 256-byte aligned
+  slot inside the region ``[owner -> destination]``; every rank computes the same layout from the
+  headers alone (all ranks parse all headers);
+* the owner fills its ``W`` outgoing regions with ONE gather launch per file
+  (``fill_ops``: shards as strided copies, replicated and pushed tensors as flat copies), writing
+  its own region straight into the receive buffer;
+* one ``all_to_all_single`` with the region sizes as split sizes moves everything; results are
+  typed views of the receive buffer.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+from . import shard_plan
+from .common import TensorFrame
+
+SLOT_ALIGN = 256
+
+Action = Tuple  # ("shard", dim) | ("replicate",) | ("push", dst_rank)
+
+
+def _align(n: int) -> int:
+    return (n + SLOT_ALIGN - 1) // SLOT_ALIGN * SLOT_ALIGN
+
+
+@dataclass
+class Slot:
+    name: str
+    offset: int          # inside the [owner -> dst] region
+    nbytes: int
+    shape: List[int]     # shape of what dst receives (safetensors element counts)
+
+
+@dataclass
+class BatchLayout:
+    """Slots of every [owner][dst] region for one batch of requests."""
+
+    world: int
+    region_bytes: List[List[int]] = field(default_factory=list)       # [owner][dst]
+    slots: List[List[List[Slot]]] = field(default_factory=list)       # [owner][dst] -> slots
+    where: Dict[str, Tuple[int, Action]] = field(default_factory=dict)  # name -> (owner, action)
+
+    def __post_init__(self) -> None:
+        w = self.world
+        self.region_bytes = [[0] * w for _ in range(w)]
+        self.slots = [[[] for _ in range(w)] for _ in range(w)]
+
+    def add(self, name: str, frame: TensorFrame, owner: int, action: Action) -> None:
+        w = self.world
+        bits = frame.dtype.bits
+        total = frame.data_offsets[1] - frame.data_offsets[0]
+        if action[0] == "shard":
+            dim = action[1]
+            shard_plan.check_even_split(name, frame.shape[dim], w)
+            shape = list(frame.shape)
+            shape[dim] = shard_plan.block_size(frame.shape[dim], w)
+            rows, row_bytes, _, _ = shard_plan.slice_geometry(frame.shape, bits, dim, 0, shape[dim])
+            targets = [(r, rows * row_bytes, shape) for r in range(w)]
+        elif action[0] == "replicate":
+            targets = [(r, total, list(frame.shape)) for r in range(w)]
+        elif action[0] == "push":
+            targets = [(action[1], total, list(frame.shape))]
+        else:
+            raise ValueError(f"unknown action {action!r} for {name}")
+        for dst, nbytes, shape in targets:
+            off = self.region_bytes[owner][dst]
+            self.slots[owner][dst].append(Slot(name, off, nbytes, shape))
+            self.region_bytes[owner][dst] = off + _align(nbytes)
+        self.where[name] = (owner, action)
+
+    # Buffers as rank `me` sees them.  The region a rank sends to itself never travels: the
+    # owner writes it straight into the tail of its receive buffer, behind what the others send.
+    def send_sizes(self, me: int) -> List[int]:
+        return [0 if d == me else self.region_bytes[me][d] for d in range(self.world)]
+
+    def recv_sizes(self, me: int) -> List[int]:
+        return [0 if o == me else self.region_bytes[o][me] for o in range(self.world)]
+
+    def recv_total(self, me: int) -> int:
+        return sum(self.recv_sizes(me)) + self.region_bytes[me][me]
+
+    def recv_offset(self, me: int, owner: int) -> int:
+        if owner == me:
+            return sum(self.recv_sizes(me))
+        return sum(self.recv_sizes(me)[:owner])
+
+    def send_offset(self, me: int, dst: int) -> int:
+        return sum(self.send_sizes(me)[:dst])
+
+    def fill_ops(self, me: int, frames: Dict[str, TensorFrame], src_addr: Dict[str, int],
+                 region_addr: Sequence[int]) -> List[shard_plan.Op]:
+        """Copies by which owner ``me`` fills its outgoing regions; ``region_addr[dst]`` is where
+        region ``[me -> dst]`` starts (the send buffer, or the receive buffer for ``dst == me``)."""
+        ops: List[shard_plan.Op] = []
+        w = self.world
+        for dst in range(w):
+            for slot in self.slots[me][dst]:
+                if slot.nbytes == 0:
+                    continue
+                frame = frames[slot.name]
+                _, action = self.where[slot.name]
+                to = region_addr[dst] + slot.offset
+                if action[0] == "shard":
+                    lo, hi = shard_plan.shard_bounds(frame.shape[action[1]], w, dst)
+                    ops.append(shard_plan.shard_op(src_addr[slot.name], to, frame.shape,
+                                                   frame.dtype.bits, action[1], lo, hi))
+                else:
+                    ops.append((src_addr[slot.name], to, 1, slot.nbytes, 0, 0))
+        return ops
+
+    def received(self, me: int) -> List[Tuple[Slot, int]]:
+        """(slot, offset in the receive buffer) of everything rank ``me`` ends up with."""
+        out: List[Tuple[Slot, int]] = []
+        for owner in range(self.world):
+            base = self.recv_offset(me, owner)
+            for slot in self.slots[owner][me]:
+                out.append((slot, base + slot.offset))
+        return out
+
+
+class ShardExchange:
+    """One batch of requests, prepared once and runnable many times.
+
+    ``local=False``: this process is rank ``me`` of ``world``; ``run()`` packs what this rank owns
+    (gather kernel) and meets the other ranks in one ``all_to_all_single``; ``results()`` are the
+    tensors this rank receives.
+
+    ``local=True``: this process owns every file and produces the data of all ``world``
+    destinations itself (no transport): ``run()`` is a single gather launch, ``results()`` is a
+    list with one ``{name: tensor}`` per destination rank.  This is the owner-side half of the
+    exchange run for all destinations at once, e.g. by a single-GPU process that prepares the
+    shards of a ``world``-way tensor-parallel group.
+    """
+
+    def __init__(self, fb, requests: "Dict[str, Action]", world: int, me: int, local: bool):
+        import torch
+
+        from . import _native as nat
+
+        self.fb, self.world, self.me, self.local = fb, world, me, local
+        self.names = list(requests)
+        self.layout = BatchLayout(world)
+        self.frames: Dict[str, TensorFrame] = {}
+        src_addr: Dict[str, int] = {}
+        self.device = next(l.device for ls in fb.rank_loaders.values() for l in ls)
+        for name in self.names:
+            rank, lidx = fb._get_rank_lidx(name)
+            loader = fb.rank_loaders[rank][lidx]
+            self.frames[name] = loader.metadata.tensors[name]
+            owner = 0 if local else rank
+            self.layout.add(name, self.frames[name], owner, requests[name])
+            if owner == me:
+                if name not in loader.tensors:
+                    raise Exception(f"exchange: tensor {name} was not found, released? lidx={loader.lidx}")
+                src_addr[name] = loader.tensors[name].data_ptr()
+        torch_dev = "cpu" if self.device.is_cpu else self.device.as_str()
+        lay = self.layout
+        if local:
+            sizes = lay.region_bytes[0]
+            self.recv = torch.empty(sum(sizes), dtype=torch.uint8, device=torch_dev)
+            self.send = None
+            region = [self.recv.data_ptr() + sum(sizes[:d]) for d in range(world)]
+        else:
+            self.recv = torch.empty(lay.recv_total(me), dtype=torch.uint8, device=torch_dev)
+            self.send = torch.empty(sum(lay.send_sizes(me)), dtype=torch.uint8, device=torch_dev)
+            region = [self.send.data_ptr() + lay.send_offset(me, d) for d in range(world)]
+            region[me] = self.recv.data_ptr() + lay.recv_offset(me, me)
+        mine = {n: f for n, f in self.frames.items() if n in src_addr}
+        ops = lay.fill_ops(me, mine, src_addr, region) if mine else []
+        self.payload_bytes = sum(o[2] * o[3] for o in ops)
+        lo, hi = self.recv.data_ptr(), self.recv.data_ptr() + self.recv.numel()
+        groups = [([o for o in ops if lo <= o[1] < hi], self.recv)]
+        if self.send is not None:
+            groups.append(([o for o in ops if not (lo <= o[1] < hi)], self.send))
+        # (ctypes op array, count, destination base, destination length) per launch
+        self.launches = [(nat.make_ops(g), len(g), buf.data_ptr(), buf.numel()) for g, buf in groups if g]
+
+    def run(self) -> None:
+        """Enqueue the gather launch(es) on torch's current stream, then the exchange."""
+        from . import _native as nat
+
+        if self.device.is_cpu:
+            for arr, n, _, _ in self.launches:
+                nat.check(nat.lib.fst_gather_host(arr, n, 8), "fst_gather_host")
+        else:
+            stream = self.fb.framework.current_stream(self.device)
+            for arr, n, base, length in self.launches:
+                nat.check(nat.lib.fst_gather(arr, n, 0, 0, base, length, stream), "fst_gather")
+        if not self.local:
+            import torch.distributed as dist
+
+            lay, me = self.layout, self.me
+            incoming = sum(lay.recv_sizes(me))
+            dist.all_to_all_single(self.recv[:incoming], self.send, lay.recv_sizes(me),
+                                   lay.send_sizes(me), group=self.fb.pg.real_pg)
+
+    def _view(self, slot: Slot, off: int):
+        from .frameworks._torch import TorchTensor, dtype_convert
+
+        frame = self.frames[slot.name]
+        native = self.fb.framework.get_native_shape(frame.dtype, slot.shape)
+        t = self.recv[off: off + slot.nbytes].view(dtype_convert[frame.dtype]).reshape(native)
+        return TorchTensor(self.device, frame.dtype, t)
+
+    def results(self):
+        lay = self.layout
+        if not self.local:
+            return {slot.name: self._view(slot, off) for slot, off in lay.received(self.me)}
+        out = []
+        sizes = lay.region_bytes[0]
+        for dst in range(self.world):
+            base = sum(sizes[:dst])
+            out.append({s.name: self._view(s, base + s.offset) for s in lay.slots[0][dst]})
+        return out

@@ -130,10 +130,67 @@ class FilesBufferOnDevice:
 
     # ------------------------------------------------------------------ many tensors
     def as_dict(self, tensor_shard_dim: "OrderedDict[str, int]") -> Dict[str, TensorBase]:
-        """``{name: wrapped tensor}`` for ``{name: dim}`` (``-1`` = replicate)."""
+        """``{name: wrapped tensor}`` for ``{name: dim}`` (``-1`` = replicate).  With more than
+        one rank the whole request is served by the batched exchange (see ``exchange``)."""
+        requests = OrderedDict(
+            (name, ("replicate",) if dim == -1 else ("shard", dim))
+            for name, dim in tensor_shard_dim.items()
+        )
+        return self.exchange(requests)
+
+    def exchange(self, requests: "OrderedDict[str, Tuple]",
+                 max_batch_bytes: int = 8 << 30) -> Dict[str, TensorBase]:
+        """Serve many requests at once: ``{name: ("shard", dim) | ("replicate",) | ("push", r)}``.
+
+        Per batch (requests are cut into batches of at most ``max_batch_bytes`` outgoing bytes
+        per owner) every owner packs all it has to send with one gather launch per destination
+        buffer and all ranks meet in ONE ``all_to_all_single``; upstream issues a collective and
+        a device synchronisation per tensor (tensor_factory.py:143,186).  Results are views of
+        the batch's receive buffer.  For a pushed tensor only the destination rank gets an
+        entry.  Every rank must pass the same requests in the same order.
+        """
+        from .batch import ShardExchange
+
+        world, me = self.pg.size(), self.pg.rank()
         out: Dict[str, TensorBase] = {}
-        for name, dim in tensor_shard_dim.items():
-            rank, lidx = self._get_rank_lidx(name)
-            out[name] = self.rank_loaders[rank][lidx].shuffle(self.pg, name, dim)
-            self._mark(rank, lidx, name)
+        if world == 1:
+            for name in requests:
+                rank, lidx = self._get_rank_lidx(name)
+                out[name] = self.rank_loaders[rank][lidx].tensors[name]
+            return out
+        for names in self._batches(requests, world, max_batch_bytes):
+            ex = ShardExchange(self, OrderedDict((n, requests[n]) for n in names), world, me, local=False)
+            ex.run()
+            out.update(ex.results())
+            for name in names:
+                self._mark(*self.key_to_rank_lidx[name], name)
         return out
+
+    def _batches(self, requests, world: int, max_batch_bytes: int) -> List[List[str]]:
+        """Cut requests (in order) so that no owner sends more than ``max_batch_bytes`` a batch."""
+        batches: List[List[str]] = [[]]
+        volume = [0] * world
+        for name, action in requests.items():
+            rank, lidx = self._get_rank_lidx(name)
+            frame = self.rank_loaders[rank][lidx].metadata.tensors[name]
+            nbytes = frame.data_offsets[1] - frame.data_offsets[0]
+            cost = nbytes * (world if action[0] == "replicate" else 1)
+            if batches[-1] and volume[rank] + cost > max_batch_bytes:
+                batches.append([])
+                volume = [0] * world
+            batches[-1].append(name)
+            volume[rank] += cost
+        return [b for b in batches if b]
+
+    def shard_locally(self, requests: "OrderedDict[str, Tuple]", world_size: int) -> List[Dict[str, TensorBase]]:
+        """Single-process form of ``exchange``: this process (which must own every file of the
+        requests, i.e. was opened with one rank) produces what each of ``world_size``
+        tensor-parallel ranks would receive, with one gather launch.  Returns one
+        ``{name: wrapped tensor}`` per destination rank; the tensors are views of one buffer."""
+        from .batch import ShardExchange
+
+        if self.pg.size() != 1:
+            raise Exception("shard_locally needs a single-rank loader (it owns every file)")
+        ex = ShardExchange(self, requests, world_size, 0, local=True)
+        ex.run()
+        return ex.results()

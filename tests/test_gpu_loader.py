@@ -1,0 +1,191 @@
+"""File -> HBM through the native reader and the loader API, on a GPU, checked against the file
+bytes, the oracle and upstream's recorded outputs."""
+
+import errno
+import os
+from collections import OrderedDict
+
+import numpy as np
+import pytest
+import torch
+
+import fastsafetensors_b200 as fst
+from fastsafetensors_b200 import _native as nat
+from fastsafetensors_b200 import cpp, shard_plan, synth
+from fastsafetensors_b200.batch import BatchLayout
+from fastsafetensors_b200.frameworks import get_framework_op
+from oracle import st_oracle
+from tests.golden import cases
+from tests.helpers import digest_bytes, record, tensor_bytes
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def blob_file(tmp_path_factory):
+    rng = np.random.default_rng(11)
+    data = rng.integers(0, 256, 37 * (1 << 20) + 4321, dtype=np.uint8)
+    p = tmp_path_factory.mktemp("blob") / "blob.bin"
+    p.write_bytes(data.tobytes())
+    return str(p), data
+
+
+@pytest.mark.parametrize("io_mode", [nat.IO_DIRECT, nat.IO_BUFFERED, nat.IO_AUTO])
+@pytest.mark.parametrize("offset", [0, 4096, 8 + 1, 8 + 4567, 123456 + 8])
+@pytest.mark.parametrize("plain_dma_only", [False, True])
+def test_reader_to_hbm(blob_file, io_mode, offset, plain_dma_only, leak_check):
+    """Even offsets take the plain DMA, odd ones the staging ring + realign kernel (or, with
+    plain_dma_only, a DMA to an unaligned address).  Slots of 1 MiB force many windows."""
+    path, data = blob_file
+    length = data.size - offset
+    before = cpp.get_cpp_metrics()
+    reader = cpp.Reader(0, 4, 1 << 20, 2, io_mode=io_mode, copy_streams=2, plain_dma_only=plain_dma_only)
+    try:
+        dst = torch.full((length + 512,), 0x5A, dtype=torch.uint8, device=DEV)
+        buf = cpp.gds_device_buffer(dst.data_ptr(), dst.numel(), True)
+        rid = reader.submit(path, offset, length, buf, 256)
+        assert reader.wait(rid, 60000) == length
+        got = dst.cpu().numpy()
+        assert np.array_equal(got[256:256 + length], data[offset:])
+        assert (got[:256] == 0x5A).all() and (got[256 + length:] == 0x5A).all()
+        after = cpp.get_cpp_metrics()
+        assert after.bytes_h2d - before.bytes_h2d == length
+        realigned = after.bytes_realigned - before.bytes_realigned
+        if offset % 16 == 0 or plain_dma_only:
+            assert realigned == 0
+        else:
+            assert realigned == length
+            assert after.staging_device_bytes > 0
+    finally:
+        reader.close()
+    assert cpp.get_cpp_metrics().staging_device_bytes == 0
+
+
+def test_reader_failure_is_reported_and_reader_survives(blob_file, leak_check):
+    path, data = blob_file
+    reader = cpp.Reader(0, 2, 1 << 20, 2, io_mode=nat.IO_BUFFERED)
+    try:
+        dst = torch.zeros(8 << 20, dtype=torch.uint8, device=DEV)
+        buf = cpp.gds_device_buffer(dst.data_ptr(), dst.numel(), True)
+        reader.inject_fault(4, errno.EIO)
+        with pytest.raises(nat.NativeError) as e:
+            reader.wait(reader.submit(path, 0, 8 << 20, buf, 0))
+        assert e.value.code == nat.EIO
+        assert reader.wait(reader.submit(path, 3, 1 << 20, buf, 0)) == 1 << 20
+        assert np.array_equal(dst[: 1 << 20].cpu().numpy(), data[3: 3 + (1 << 20)])
+    finally:
+        reader.close()
+
+
+# ------------------------------------------------------------------ loader on cuda, one rank
+SINGLE = [c for c in cases.CASES if c["world"] == 1]
+
+
+@pytest.mark.parametrize("case", SINGLE, ids=[c["id"] for c in SINGLE])
+def test_loader_cuda_single_rank_matches_upstream(case, golden, case_files, leak_check):
+    paths = case_files(case)
+    want = golden["cases"][case["id"]][0]
+    loader = fst.SafeTensorsFileLoader(fst.SingleGroup(), torch.device(DEV), nogds=case.get("nogds", True),
+                                       max_threads=4, slot_kb=64)
+    loader.add_filenames({0: paths})
+    fb = loader.copy_files_to_device()
+    got = {}
+    for step in case["steps"]:
+        if step[0] == "plan":
+            for name, action in cases.plan(case):
+                if action[0] == "shard":
+                    t = fb.get_sharded(name, action[1])
+                elif action[0] == "replicate":
+                    t = fb.get_tensor(name)
+                else:
+                    t = fb.push_tensor(name, 0)
+                assert t.is_cuda
+                got[name] = record(t)
+        elif step[0] == "multi_cols":
+            got[step[1]] = record(fb.get_multi_cols(step[2], step[3]))
+    assert got == want
+    fb.close()
+    loader.close()
+
+
+def test_odd_header_goes_through_the_realign_kernel(case_files, leak_check):
+    """llama2-13b twin: header length is odd, so host and device addresses are never congruent
+    modulo 16 and every window is shifted by the kernel; tensors stay byte-identical."""
+    case = [c for c in cases.CASES if c["id"] == "llama2_13b_w4"][0]
+    paths = case_files(case)
+    before = cpp.get_cpp_metrics()
+    with fst.fastsafe_open(paths, device=DEV, nogds=True) as f:
+        mid = cpp.get_cpp_metrics()
+        total = sum(os.path.getsize(p) - st_oracle.FileOracle(p).header_length for p in paths)
+        assert mid.bytes_realigned - before.bytes_realigned == total
+        for p in paths:
+            fo = st_oracle.FileOracle(p)
+            assert fo.header_length % 2 == 1
+            for name in fo.tensors:
+                t = f.get_tensor(name)
+                assert t.data_ptr() % 2 == 0
+                assert digest_bytes(tensor_bytes(t)) == digest_bytes(fo.raw(name)), name
+
+
+# ------------------------------------------------------------------ owner-side packing for W ranks
+MULTI = [c for c in cases.CASES if c["world"] > 1 and c["steps"][0][0] == "plan"]
+
+
+@pytest.mark.parametrize("case", MULTI, ids=[c["id"] for c in MULTI])
+def test_owner_packing_for_all_ranks_matches_upstream(case, golden, case_files, leak_check):
+    """One GPU plays every owner in turn: for each file it builds the batch layout of the whole
+    plan, fills all W outgoing regions with the gather kernel, and each region must hold exactly
+    what upstream delivered to that rank (the transport that follows only moves the regions)."""
+    paths = sorted(case_files(case))
+    world = case["world"]
+    plan = OrderedDict((n, (a[0], a[1] % world) if a[0] == "push" else a) for n, a in cases.plan(case))
+    loader = fst.SafeTensorsFileLoader(fst.SingleGroup(), DEV, nogds=True, max_threads=4, slot_kb=256)
+    loader.add_filenames({0: paths})
+    fb = loader.copy_files_to_device()
+    layout = BatchLayout(world)
+    frames, src_addr = {}, {}
+    for name, action in plan.items():
+        _, lidx = fb.key_to_rank_lidx[name]
+        factory = fb.rank_loaders[0][lidx]
+        frames[name] = factory.metadata.tensors[name]
+        src_addr[name] = factory.tensors[name].data_ptr()
+        layout.add(name, frames[name], lidx % world, action)
+    stream = int(torch.cuda.current_stream().cuda_stream)
+    for owner in range(world):
+        sizes = layout.region_bytes[owner]
+        buf = torch.zeros(max(1, sum(sizes)), dtype=torch.uint8, device=DEV)
+        region = [buf.data_ptr() + sum(sizes[:d]) for d in range(world)]
+        mine = {n: f for n, f in frames.items() if layout.where[n][0] == owner}
+        nat.gather(layout.fill_ops(owner, mine, src_addr, region), stream, (0, 0), (buf.data_ptr(), buf.numel()))
+        host = buf.cpu().numpy()
+        for dst in range(world):
+            base = sum(sizes[:dst])
+            for slot in layout.slots[owner][dst]:
+                rec = golden["cases"][case["id"]][dst][slot.name]
+                assert rec is not None and rec[0] == slot.shape, slot.name
+                assert digest_bytes(host[base + slot.offset: base + slot.offset + slot.nbytes]) == rec[2], \
+                    (slot.name, owner, dst)
+    fb.close()
+    loader.close()
+
+
+def test_full_size_tensors_by_properties():
+    """Llama-3-8B sized tensors (too big for the golden file): a dim-1 shard pack must be a
+    permutation that preserves the multiset of 8-byte words per row block, and the oracle on a
+    sample of rows must agree bit for bit."""
+    shape, world, bits = (4096, 14336), 8, 16
+    g = torch.Generator(device=DEV).manual_seed(5)
+    t = torch.randint(0, 1 << 15, shape, dtype=torch.int16, device=DEV, generator=g)
+    n = t.numel() * 2
+    ops, shard_bytes = shard_plan.scatter_ops(t.data_ptr(), 0, shape, bits, 1, world)
+    packed = torch.empty(n, dtype=torch.uint8, device=DEV)
+    nat.gather([(o[0], o[1] + packed.data_ptr()) + o[2:] for o in ops],
+               int(torch.cuda.current_stream().cuda_stream), (t.data_ptr(), n), (packed.data_ptr(), n))
+    assert int(packed.view(torch.int64).sum()) == int(t.view(torch.int64).sum())  # checksum of checksums
+    want = torch.cat([c.contiguous().reshape(-1) for c in t.chunk(world, dim=1)])
+    assert torch.equal(packed.view(torch.int16), want)
+    raw = t[:64].cpu().numpy().view(np.uint8).reshape(-1)
+    got0 = packed[: shard_bytes].view(torch.int16).reshape(4096, -1)[:64].cpu().numpy().view(np.uint8).reshape(-1)
+    want0, _ = st_oracle.shard(raw, (64, 14336), "BF16", 1, 0, world)
+    assert np.array_equal(got0, want0)

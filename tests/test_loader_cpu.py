@@ -241,3 +241,24 @@ def test_missing_key_and_missing_file():
     with pytest.raises(Exception):
         loader.add_filenames({0: ["/nonexistent/file.safetensors"]})
     loader.close()
+
+
+MULTI_PLAN = [c for c in cases.CASES if c["world"] > 1 and c["steps"][0][0] == "plan"]
+
+
+@pytest.mark.parametrize("case", MULTI_PLAN, ids=[c["id"] for c in MULTI_PLAN])
+def test_shard_locally_produces_every_ranks_tensors(case, golden, case_files, leak_check):
+    """One process owning all files produces what each of W ranks received from upstream."""
+    paths = case_files(case)
+    world = case["world"]
+    plan = OrderedDict((n, (a[0], a[1] % world) if a[0] == "push" else a) for n, a in cases.plan(case))
+    loader = fst.SafeTensorsFileLoader(fst.SingleGroup(), "cpu", nogds=True, max_threads=4, slot_kb=64)
+    loader.add_filenames({0: paths})
+    fb = loader.copy_files_to_device()
+    per_rank = fb.shard_locally(plan, world)
+    assert len(per_rank) == world
+    for rank, tensors in enumerate(per_rank):
+        want = {k: v for k, v in golden["cases"][case["id"]][rank].items() if v is not None}
+        assert {k: record(v) for k, v in tensors.items()} == want
+    fb.close()
+    loader.close()

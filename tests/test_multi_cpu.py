@@ -16,7 +16,7 @@ from tests.golden import cases
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _rank_main(rank, world, case, paths, port, out_dir):
+def _rank_main(rank, world, case, paths, port, out_dir, batched=False):
     sys.path.insert(0, ROOT)
     import fastsafetensors_b200 as fst
     from fastsafetensors_b200 import cpp
@@ -29,7 +29,17 @@ def _rank_main(rank, world, case, paths, port, out_dir):
     fb = loader.copy_files_to_device()
     out = {}
     for step in case["steps"]:
-        if step[0] == "plan":
+        if step[0] == "plan" and batched:
+            # the whole plan in one batched exchange (tiny batches force several rounds)
+            plan = OrderedDict((n, (a[0], a[1] % world) if a[0] == "push" else a) for n, a in cases.plan(case))
+            got = fb.exchange(plan, max_batch_bytes=1 << 20)
+            for name, action in plan.items():
+                if action[0] == "push" and action[1] != rank:
+                    assert name not in got
+                    out[name] = None
+                else:
+                    out[name] = record(got[name])
+        elif step[0] == "plan":
             for name, action in cases.plan(case):
                 if action[0] == "shard":
                     out[name] = record(fb.get_sharded(name, action[1]))
@@ -44,7 +54,7 @@ def _rank_main(rank, world, case, paths, port, out_dir):
             for name, t in fb.as_dict(OrderedDict(step[1])).items():
                 out["as_dict:" + name] = record(t)
     # every file was requested in full by the "plan" step: its image must be gone already
-    if case["steps"] == [("plan",)] and not case.get("skip"):
+    if list(case["steps"]) == [("plan",)] and not case.get("skip"):
         assert all(f.gbuf is None for fs in fb.rank_loaders.values() for f in fs)
     fb.close()
     loader.close()
@@ -59,12 +69,15 @@ MULTI = [c for c in cases.CASES if c["world"] > 1 and c["id"] in
          ("llama3_8b_w2_cols", "llama2_13b_w4", "mixtral_w8", "crafted_w2")]
 
 
+@pytest.mark.parametrize("batched", [False, True], ids=["per_tensor", "batched"])
 @pytest.mark.parametrize("case", MULTI, ids=[c["id"] for c in MULTI])
-def test_gloo_ranks_match_upstream(case, golden, case_files, tmp_path):
+def test_gloo_ranks_match_upstream(case, batched, golden, case_files, tmp_path):
+    if batched and case["steps"][0][0] != "plan":
+        pytest.skip("as_dict in the per-tensor run already goes through the batched exchange")
     paths = case_files(case)
     world = case["world"]
-    port = 29700 + cases.CASES.index(case)
-    mp.spawn(_rank_main, args=(world, case, paths, port, str(tmp_path)), nprocs=world, join=True)
+    port = 29700 + 2 * cases.CASES.index(case) + int(batched)
+    mp.spawn(_rank_main, args=(world, case, paths, port, str(tmp_path), batched), nprocs=world, join=True)
     for rank in range(world):
         got = json.load(open(tmp_path / f"rank{rank}.json"))
         assert got == golden["cases"][case["id"]][rank], f"rank {rank}"

@@ -1,6 +1,6 @@
 """Builds ``libfst_b200.so`` in-tree with nvcc for sm_100a.
 
-``python -m fastsafetensors_b200._build`` (or ``build_native()``) compiles the three sources in
+``python fastsafetensors_b200/_build.py`` (or ``build_native()``) compiles the three sources in
 ``csrc/`` into ``fastsafetensors_b200/libfst_b200.so``.  The build is skipped when the library
 is newer than every source and header.  nvcc cross-compiles without a GPU, so this also runs on
 a machine that has none.

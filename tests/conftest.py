@@ -12,8 +12,12 @@ if ROOT not in sys.path:
 
 # The native library must exist before the package can be imported.  Building is part of the
 # test set-up (nvcc cross-compiles without a GPU); using a stale or missing library is not.
-from fastsafetensors_b200 import _build  # noqa: E402
+import importlib.util  # noqa: E402
 
+_spec = importlib.util.spec_from_file_location(
+    "fst_b200_build", os.path.join(ROOT, "fastsafetensors_b200", "_build.py"))
+_build = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(_build)  # loaded by path: importing the package needs the library
 _build.build_native()
 
 GOLDEN_PATH = os.path.join(ROOT, "tests", "golden", "reference_outputs.json")

@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--dir", default=os.environ.get("FST_BENCH_DIR", "/tmp/fst_bench"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="keep only the first L transformer layers (small case for profiler captures)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the device-resident phase (for profiler captures)")
     return ap.parse_args()
@@ -125,6 +127,22 @@ def read_into_page_cache(paths) -> None:
                 pass
 
 
+def load_spec(args):
+    """The checkpoint spec of the run; ``--layers L`` cuts it to the first L layers."""
+    import re
+
+    from fastsafetensors_b200 import synth
+
+    spec = synth.config(args.config, args.scale)
+    if args.layers > 0:
+        def keep(name: str) -> bool:
+            m = re.search(r"(?:layers|h)\.(\d+)\.", name)
+            return m is None or int(m.group(1)) < args.layers
+        spec.tensors = [t for t in spec.tensors if keep(t.name)]
+        spec.name = f"{spec.name}-first{args.layers}layers"
+    return spec
+
+
 def prepare_files(spec, directory: str, rank: int, barrier) -> list:
     from fastsafetensors_b200 import synth
 
@@ -172,7 +190,7 @@ def b200_arm(args) -> dict:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    spec = synth.config(args.config, args.scale)
+    spec = load_spec(args)
     tp = spec.tp if world == 1 else world
     plan = plan_for(spec, tp)
     paths = prepare_files(spec, args.dir, rank, barrier)
@@ -196,7 +214,8 @@ def b200_arm(args) -> dict:
     # for at least 1.5 s so that the short timed region is bracketed by samples taken under load
     sampler = ClockSampler(local_rank) if rank == 0 else None
     warm_t0, warm_steps = time.perf_counter(), 0
-    while warm_steps < max(3, args.warmup) or time.perf_counter() - warm_t0 < 1.5:
+    min_warm_s = 0.0 if args.kernel_only else 1.5
+    while warm_steps < max(3, args.warmup) or time.perf_counter() - warm_t0 < min_warm_s:
         ex.run()
         warm_steps += 1
         if warm_steps % 8 == 0:
@@ -475,7 +494,7 @@ def reference_arm(args) -> dict:
     rank, _, world = dist_env()
     if rank != 0:
         return {}
-    spec = synth.config(args.config, args.scale)
+    spec = load_spec(args)
     tp = spec.tp if world == 1 else world
     paths = prepare_files(spec, args.dir, 0, lambda: None)
     phases = [("cold", True, args.steps, 1), ("warm", False, min(args.steps, 3), 1)]

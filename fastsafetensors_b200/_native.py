@@ -2,7 +2,7 @@
 
 The library is loaded from the package directory only.  If it is missing the import of this
 module raises: there is no pure-Python or torch substitute for the native layer.  Build it with
-``python -m fastsafetensors_b200._build``.
+``python fastsafetensors_b200/_build.py``.
 """
 
 from __future__ import annotations
@@ -32,6 +32,7 @@ OK, EINVAL, ERANGE, ENOCUDA, ECUDA, EIO, ETIMEOUT, ENOMEM, ELIMIT, EGDS = (
 )
 IO_AUTO, IO_DIRECT, IO_BUFFERED = 0, 1, 2
 GATHER_INLINE_OPS = 48
+GATHER_STATIC_MAX_OPS = 4096
 
 # every symbol the header declares; tests check that the library exports each one
 EXPORTS = (
@@ -39,8 +40,8 @@ EXPORTS = (
     "fst_device_pci_bus", "fst_device_numa_node", "fst_pin_numa", "fst_host_alloc",
     "fst_host_free", "fst_read_host", "fst_io_alignment", "fst_get_metrics",
     "fst_reader_create", "fst_reader_submit", "fst_reader_wait", "fst_reader_destroy",
-    "fst_reader_inject_fault", "fst_gather", "fst_gather_host", "fst_realign",
-    "fst_release_workspaces",
+    "fst_reader_inject_fault", "fst_gather", "fst_gather_static", "fst_gather_host",
+    "fst_realign", "fst_release_workspaces",
 )
 
 
@@ -97,7 +98,7 @@ def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
             f"{LIB_PATH} is missing: the native CUDA layer has not been built "
-            "(run `python -m fastsafetensors_b200._build`); there is no fallback"
+            "(run `python fastsafetensors_b200/_build.py`); there is no fallback"
         )
     lib = ctypes.CDLL(LIB_PATH)
     lib.fst_abi_version.restype = c_int
@@ -125,6 +126,7 @@ def _load() -> ctypes.CDLL:
     lib.fst_gather.argtypes = [
         POINTER(Copy2D), c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64,
     ]
+    lib.fst_gather_static.argtypes = lib.fst_gather.argtypes
     lib.fst_gather_host.argtypes = [POINTER(Copy2D), c_uint64, c_int]
     lib.fst_realign.argtypes = [c_uint64, c_uint64, c_uint64, c_uint64]
     lib.fst_release_workspaces.restype = c_int
@@ -179,6 +181,20 @@ def gather(ops: Sequence[Tuple[int, int, int, int, int, int]], stream: int,
     check(
         lib.fst_gather(arr, len(ops), src_span[0], src_span[1], dst_span[0], dst_span[1], stream),
         "fst_gather",
+    )
+
+
+def gather_static(ops: Sequence[Tuple[int, int, int, int, int, int]], stream: int,
+                  src_span: Tuple[int, int] = (0, 0), dst_span: Tuple[int, int] = (0, 0)) -> None:
+    """``fst_gather_static``: the device gather with its op table in a fixed array of the
+    library (at most ``GATHER_STATIC_MAX_OPS`` ops); allocates nothing.  Calls on different
+    streams must not overlap."""
+    if not ops:
+        return
+    arr = make_ops(ops)
+    check(
+        lib.fst_gather_static(arr, len(ops), src_span[0], src_span[1], dst_span[0], dst_span[1], stream),
+        "fst_gather_static",
     )
 
 

@@ -566,3 +566,109 @@ extern "C" int fst_release_workspaces(void) {
     cudaSetDevice(cur);
     return FST_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// fst_gather_static: the gather for callers that cannot allocate
+// ------------------------------------------------------------------------------------------
+namespace fst {
+namespace {
+
+// The op table of fst_gather_static.  Part of the library image: every GPU that loads the
+// library holds these 256 KiB until the process exits.  In host code this name is only a
+// handle for cudaGetSymbolAddress, never an address a kernel may be given.
+static __device__ __align__(256) GatherOp g_static_table[FST_GATHER_STATIC_MAX_OPS];
+
+// Host-side twin in which the records are assembled (fixed storage, no heap), and the device
+// address of the table per device (looked up once, with that device current).
+GatherOp g_static_host[FST_GATHER_STATIC_MAX_OPS];
+GatherOp *g_static_dev[MAX_DEVICES];
+
+}  // namespace
+}  // namespace fst
+
+extern "C" int fst_gather_static(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_base,
+                                 uint64_t src_len, uint64_t dst_base, uint64_t dst_len,
+                                 uint64_t stream) {
+    using namespace fst;
+    clear_error();
+    if (!cuda_usable()) {
+        set_error("fst_gather_static: no CUDA device");
+        return FST_ENOCUDA;
+    }
+    if (n_ops == 0) return FST_OK;
+    if (ops == nullptr) {
+        set_error("fst_gather_static: ops is null");
+        return FST_EINVAL;
+    }
+    if (n_ops > FST_GATHER_STATIC_MAX_OPS) {
+        set_error("fst_gather_static: %llu ops exceed the fixed table of %d; split the request",
+                  (unsigned long long)n_ops, FST_GATHER_STATIC_MAX_OPS);
+        return FST_ELIMIT;
+    }
+    int rc = check_ops(ops, n_ops, src_base, src_len, dst_base, dst_len);
+    if (rc != FST_OK) return rc;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= MAX_DEVICES) {
+        set_error("fst_gather_static: device index %d not supported", dev);
+        return FST_ELIMIT;
+    }
+    // one lock for the shared host twin, the per-device address cache and the grid-size cache
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    if (g_static_dev[dev] == nullptr) {
+        GatherOp *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void **)&p, g_static_table);
+        if (e != cudaSuccess || p == nullptr) {
+            (void)cudaGetLastError();
+            set_error("fst_gather_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+                      cudaGetErrorString(e));
+            return FST_ECUDA;
+        }
+        g_static_dev[dev] = p;
+    }
+    // build the records in the fixed host twin (same rules as fst_gather's table)
+    unsigned count = 0;
+    uint64_t subs = 0, payload = 0;
+    for (uint64_t i = 0; i < n_ops; ++i) {
+        fst_copy2d_t c = ops[i];
+        if (c.rows == 0 || c.row_bytes == 0) continue;
+        if (c.rows > 1 && c.src_pitch == c.row_bytes && c.dst_pitch == c.row_bytes) {
+            c.row_bytes *= c.rows;
+            c.rows = 1;
+        }
+        GatherOp &g = g_static_host[count++];
+        g.src = c.src;
+        g.dst = c.dst;
+        g.src_pitch = c.rows > 1 ? c.src_pitch : 0;
+        g.dst_pitch = c.rows > 1 ? c.dst_pitch : 0;
+        g.row_bytes = c.row_bytes;
+        g.lead = (g.dst_pitch % 16 == 0) ? (uint32_t)(c.dst & 15u) : 0u;
+        const uint64_t spr = (c.row_bytes + g.lead + SUB_BYTES - 1) / SUB_BYTES;
+        g.subs_per_row = (uint32_t)spr;
+        g.first_sub = subs;
+        g.n_subs = c.rows * spr;
+        subs += g.n_subs;
+        payload += c.rows * c.row_bytes;
+    }
+    if (count == 0) return FST_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    GatherOp *table = g_static_dev[dev];
+    cudaError_t e = cudaMemcpyAsync(table, g_static_host, count * sizeof(GatherOp),
+                                    cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) {
+        set_error("fst_gather_static: op table upload failed: %s", cudaGetErrorString(e));
+        return FST_ECUDA;
+    }
+    InlineOps none;
+    std::memset(&none, 0, sizeof(none));
+    fst_gather_kernel<false><<<grid_for(subs, grid_limit_for(dev)), CTA_THREADS, 0, st>>>(
+        none, table, count, subs);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("fst_gather_static: launch failed: %s", cudaGetErrorString(e));
+        return FST_ECUDA;
+    }
+    g_counters.kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    g_counters.bytes_gathered.fetch_add(payload, std::memory_order_relaxed);
+    return FST_OK;
+}

@@ -196,6 +196,38 @@ typedef struct fst_copy2d {
 int fst_gather(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_base, uint64_t src_len,
                uint64_t dst_base, uint64_t dst_len, uint64_t stream);
 
+/* fst_gather for callers that must not allocate.  (No counterpart in upstream: its native
+ * layer has no kernels and therefore no kernel workspace.)
+ *
+ * Who needs it: a loader that runs inside a process whose device memory is already spoken for --
+ * an inference server that has handed all free HBM to its KV-cache pool, or a host application
+ * that forbids the CUDA allocator after start-up because cudaMalloc/cudaFree synchronise the
+ * whole device and would stall the streams that are serving requests.  For such callers the
+ * workspace that fst_gather allocates on first use for large op tables can fail or is not
+ * allowed at all.
+ *
+ * This entry point does the same copies with the same kernel but keeps its op table in a fixed
+ * array that is part of the library image: a file-scope `static __device__` array of
+ * FST_GATHER_STATIC_MAX_OPS records (64 bytes each, 256 KiB), which every GPU that loads the
+ * library holds until the process exits.  It calls no cudaMalloc, cudaFree, cudaHostAlloc or any
+ * other allocating routine, on the device or on the host.
+ *
+ *   - n_ops > FST_GATHER_STATIC_MAX_OPS is refused with FST_ELIMIT (split the request).
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and keeps it; make that first call before
+ *     any stream capture begins.
+ *   - All calls on a device share the one array.  A call overwrites the entries it uses and
+ *     never reads beyond them, so nothing needs clearing between calls; but a call must not be
+ *     issued while an earlier call on ANOTHER stream may still be running, or the earlier kernel
+ *     can read a half-rewritten table.  Calls on one stream are ordered and safe.
+ *   - The table is uploaded with cudaMemcpyAsync from ordinary (pageable) host memory, which
+ *     returns once the runtime has staged the bytes, so the caller's ops array may be reused
+ *     as soon as the call returns.
+ * Arguments, checks and results are those of fst_gather. */
+#define FST_GATHER_STATIC_MAX_OPS 4096
+int fst_gather_static(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_base,
+                      uint64_t src_len, uint64_t dst_base, uint64_t dst_len, uint64_t stream);
+
 /* The same copies done by host threads, for buffers in host memory (device "cpu").  This is
  * the loader's CPU mode, not a substitute for fst_gather on device buffers. */
 int fst_gather_host(const fst_copy2d_t *ops, uint64_t n_ops, int threads);

@@ -1,0 +1,31 @@
+"""Multi-GPU path: one process per GPU over NCCL, checked against upstream's recorded per-rank
+outputs.  Cases run when the box has at least as many GPUs as the case has ranks."""
+
+import json
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from tests.golden import cases
+from tests.test_multi_cpu import _rank_main
+
+pytestmark = pytest.mark.gpu
+MULTI = [c for c in cases.CASES if c["world"] > 1]
+
+
+@pytest.mark.parametrize("batched", [False, True], ids=["per_tensor", "batched"])
+@pytest.mark.parametrize("case", MULTI, ids=[c["id"] for c in MULTI])
+def test_nccl_ranks_match_upstream(case, batched, golden, case_files, tmp_path):
+    world = case["world"]
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    if batched and case["steps"][0][0] != "plan":
+        pytest.skip("as_dict in the per-tensor run already goes through the batched exchange")
+    paths = case_files(case)
+    port = 29900 + 2 * cases.CASES.index(case) + int(batched)
+    mp.spawn(_rank_main, args=(world, case, paths, port, str(tmp_path), batched, "nccl"),
+             nprocs=world, join=True)
+    for rank in range(world):
+        got = json.load(open(tmp_path / f"rank{rank}.json"))
+        assert got == golden["cases"][case["id"]][rank], f"rank {rank}"

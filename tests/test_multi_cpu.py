@@ -16,15 +16,22 @@ from tests.golden import cases
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _rank_main(rank, world, case, paths, port, out_dir, batched=False):
+def _rank_main(rank, world, case, paths, port, out_dir, batched=False, backend="gloo"):
     sys.path.insert(0, ROOT)
     import fastsafetensors_b200 as fst
     from fastsafetensors_b200 import cpp
     from tests.helpers import record
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
-    loader = fst.SafeTensorsFileLoader(dist.group.WORLD, "cpu", nogds=True, max_threads=2, slot_kb=64)
+    if backend == "nccl":
+        torch.cuda.set_device(rank)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+        device = f"cuda:{rank}"
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        device = "cpu"
+    loader = fst.SafeTensorsFileLoader(dist.group.WORLD, device, nogds=True, max_threads=2, slot_kb=64)
     loader.add_filenames(cases.owners(paths, world))
     fb = loader.copy_files_to_device()
     out = {}

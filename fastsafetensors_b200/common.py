@@ -307,3 +307,9 @@ class SafeTensorsMetadata:
                 frame.dtype = dtype
             out[name] = TorchTensor(device, frame.dtype, t)
         return out
+
+
+def resolve_cudart_lib_name() -> str:
+    """Upstream resolves which CUDA runtime to ``dlopen``; here the runtime is linked into the
+    native library, so there is nothing to resolve."""
+    return ""

@@ -18,7 +18,7 @@ from typing import Any, Dict, Optional
 
 from .. import _native as nat
 from ..common import SafeTensorsMetadata, get_device_numa_node
-from ..cpp import Reader, gds_device_buffer
+from ..cpp import Reader, gds_device_buffer, gds_file_reader
 from ..st_types import Device, DeviceType, DType
 from .base import CopierInterface
 from .registry import CopierConstructFunc, register_copier_constructor
@@ -31,7 +31,11 @@ class B200FileCopier(CopierInterface):
     def __init__(self, metadata: SafeTensorsMetadata, device: Device, reader: Reader, framework):
         self.metadata = metadata
         self.device = device
-        self.reader = reader
+        # upstream's reader objects (cpp.nogds_file_reader / cpp.gds_file_reader) are accepted
+        # too: they wrap a native reader
+        if isinstance(reader, gds_file_reader):
+            reader = reader._reader(False)
+        self.reader = getattr(reader, "_reader", reader)
         self.framework = framework
         self.request: Optional[int] = None
         if not os.path.isfile(metadata.src):

@@ -125,7 +125,8 @@ class Reader {
     void shutdown();
 
   private:
-    int start();  // allocate ring, streams, threads (first submit)
+    int start();  // streams, events, threads (first submit)
+    int ensure_ring();
     void worker(int index);
     void run_task(const Task &t, Slot &slot, int worker_index);
     ssize_t do_pread(int fd, void *buf, size_t len, off_t off);
@@ -142,6 +143,7 @@ class Reader {
     std::vector<cudaStream_t> streams_;
     std::vector<std::thread> threads_;
 
+    std::mutex ring_mu_;
     std::mutex mu_;
     std::condition_variable work_cv_;   // workers wait for tasks
     std::condition_variable done_cv_;   // waiters wait for requests
@@ -155,17 +157,12 @@ class Reader {
 int Reader::start() {
     if (started_) return FST_OK;
     const int nslots = cfg_.threads * cfg_.slots_per_thread;
-    ring_bytes_ = (uint64_t)nslots * cfg_.slot_bytes;
     if (cfg_.device >= 0) {
         cudaError_t e = cudaSetDevice(cfg_.device);
-        if (e == cudaSuccess) e = cudaHostAlloc((void **)&ring_, ring_bytes_, cudaHostAllocDefault);
         if (e != cudaSuccess) {
-            set_error("reader: cudaHostAlloc(%llu) failed: %s", (unsigned long long)ring_bytes_,
-                      cudaGetErrorString(e));
-            ring_ = nullptr;
-            return FST_ENOMEM;
+            set_error("reader: cudaSetDevice(%d) failed: %s", cfg_.device, cudaGetErrorString(e));
+            return FST_ECUDA;
         }
-        ring_pinned_ = true;
         streams_.resize(cfg_.copy_streams);
         for (auto &s : streams_) {
             e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
@@ -174,6 +171,42 @@ int Reader::start() {
                 return FST_ECUDA;
             }
         }
+    }
+    slots_.resize(nslots);
+    if (cfg_.device >= 0) {
+        for (int i = 0; i < nslots; ++i) {
+            const cudaError_t e = cudaEventCreateWithFlags(&slots_[i].done, cudaEventDisableTiming);
+            if (e != cudaSuccess) {
+                set_error("reader: cudaEventCreate failed: %s", cudaGetErrorString(e));
+                return FST_ECUDA;
+            }
+        }
+        // a device destination always goes through the ring: allocate it now, on the caller's
+        // thread, so that a failure is reported by submit
+        const int rc = ensure_ring();
+        if (rc != FST_OK) return rc;
+    }
+    started_ = true;
+    for (int i = 0; i < cfg_.threads; ++i) threads_.emplace_back(&Reader::worker, this, i);
+    return FST_OK;
+}
+
+// Allocates the slot ring on first need.  A host destination read through the page cache is
+// filled in place and never needs it.  Callers hold no lock; ring_mu_ serialises the workers.
+int Reader::ensure_ring() {
+    std::lock_guard<std::mutex> lock(ring_mu_);
+    if (ring_ != nullptr) return FST_OK;
+    const int nslots = cfg_.threads * cfg_.slots_per_thread;
+    ring_bytes_ = (uint64_t)nslots * cfg_.slot_bytes;
+    if (cfg_.device >= 0) {
+        const cudaError_t e = cudaHostAlloc((void **)&ring_, ring_bytes_, cudaHostAllocDefault);
+        if (e != cudaSuccess) {
+            set_error("reader: cudaHostAlloc(%llu) failed: %s", (unsigned long long)ring_bytes_,
+                      cudaGetErrorString(e));
+            ring_ = nullptr;
+            return FST_ENOMEM;
+        }
+        ring_pinned_ = true;
     } else {
         void *p = nullptr;
         if (posix_memalign(&p, IO_ALIGN, ring_bytes_) != 0) {
@@ -184,19 +217,7 @@ int Reader::start() {
         ring_ = (unsigned char *)p;
     }
     g_counters.bounce_buffer_bytes.fetch_add(ring_bytes_);
-    slots_.resize(nslots);
-    for (int i = 0; i < nslots; ++i) {
-        slots_[i].host = ring_ + (uint64_t)i * cfg_.slot_bytes;
-        if (cfg_.device >= 0) {
-            const cudaError_t e = cudaEventCreateWithFlags(&slots_[i].done, cudaEventDisableTiming);
-            if (e != cudaSuccess) {
-                set_error("reader: cudaEventCreate failed: %s", cudaGetErrorString(e));
-                return FST_ECUDA;
-            }
-        }
-    }
-    started_ = true;
-    for (int i = 0; i < cfg_.threads; ++i) threads_.emplace_back(&Reader::worker, this, i);
+    for (int i = 0; i < nslots; ++i) slots_[i].host = ring_ + (uint64_t)i * cfg_.slot_bytes;
     FST_DEBUG("reader: ring of %d x %llu bytes (%s), %d threads, %d streams", nslots,
               (unsigned long long)cfg_.slot_bytes, ring_pinned_ ? "pinned" : "pageable",
               cfg_.threads, (int)streams_.size());
@@ -365,6 +386,13 @@ void Reader::run_task(const Task &t, Slot &slot, int worker_index) {
         want_off = t.valid_off;
         want_len = t.valid_len;
         in_place = true;
+    }
+    if (!in_place && slot.host == nullptr) {
+        if (ensure_ring() != FST_OK) {
+            finish(t, FST_ENOMEM, "ring allocation failed", 0);
+            return;
+        }
+        buf = slot.host;
     }
     if (slot.pending) {
         cudaEventSynchronize(slot.done);

@@ -18,8 +18,6 @@ from __future__ import annotations
 
 from typing import Any, Dict, List, Optional
 
-import torch
-
 from . import _native as nat
 from . import shard_plan
 from .common import SafeTensorsMetadata, init_logger
@@ -73,7 +71,9 @@ class LazyTensorFactory:
             raise Exception(f"{what}: tensor {tensor_name} was not found, released? lidx={self.lidx}")
         return self.tensors[tensor_name]
 
-    def _bytes_buffer(self, nbytes: int) -> torch.Tensor:
+    def _bytes_buffer(self, nbytes: int):
+        import torch
+
         return torch.empty(nbytes, dtype=torch.uint8,
                            device=self.device.as_str() if not self.device.is_cpu else "cpu")
 
@@ -89,7 +89,7 @@ class LazyTensorFactory:
             return (0, 0)
         return (self.gbuf.get_base_address(), self.gbuf.get_length())
 
-    def _rows_of(self, packed: torch.Tensor, world_size: int) -> List[TorchTensor]:
+    def _rows_of(self, packed, world_size: int) -> List[TorchTensor]:
         per_rank = packed.numel() // world_size
         return [TorchTensor(self.device, DType.U8, packed[r * per_rank:(r + 1) * per_rank])
                 for r in range(world_size)]
@@ -149,6 +149,8 @@ class LazyTensorFactory:
                 rows = shard_plan.slice_geometry(frame.shape, frame.dtype.bits, dim, 0, block)[0]
                 if rows == 1:
                     # shards are contiguous in the image: scatter them as they lie
+                    import torch
+
                     flat = t.get_raw().reshape(-1).view(torch.uint8)
                     chunks = self._rows_of(flat, world)
                 else:

@@ -176,7 +176,10 @@ def b200_arm(args) -> dict:
     device = f"cuda:{local_rank}"
     pg = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device(device))
+        import datetime
+
+        dist.init_process_group("nccl", device_id=torch.device(device),
+                                timeout=datetime.timedelta(seconds=180))
         pg = dist.group.WORLD
 
     def barrier():
@@ -213,12 +216,17 @@ def b200_arm(args) -> dict:
     # clocks are sampled every 200 ms from here to the end of the timed region; the warm-up runs
     # for at least 1.5 s so that the short timed region is bracketed by samples taken under load
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    warm_t0, warm_steps = time.perf_counter(), 0
-    min_warm_s = 0.0 if args.kernel_only else 1.5
-    while warm_steps < max(3, args.warmup) or time.perf_counter() - warm_t0 < min_warm_s:
+    # every rank must run the same number of steps (each step ends in a collective when N > 1):
+    # time the first warm-up steps, then agree on how many more fill the 1.5 s
+    t_w = time.perf_counter()
+    for _ in range(max(3, args.warmup)):
         ex.run()
-        warm_steps += 1
-        if warm_steps % 8 == 0:
+    torch.cuda.synchronize()
+    per_step = (time.perf_counter() - t_w) / max(3, args.warmup)
+    extra = 0 if args.kernel_only else int(max_over_ranks(min(2000.0, 1.5 / max(per_step, 1e-6))))
+    for i in range(extra):
+        ex.run()
+        if i % 8 == 7:
             torch.cuda.synchronize()
     torch.cuda.synchronize()
     barrier()

@@ -12,10 +12,11 @@ __version__ = "0.1.0"
 from .common import SafeTensorsMetadata, SingleGroup, TensorFrame, get_device_numa_node
 from .file_buffer import FilesBufferOnDevice
 from .loader import BaseSafeTensorsFileLoader, SafeTensorsFileLoader, fastsafe_open
+from .parallel_loader import ParallelLoader, PipelineParallel
 from .st_types import Device, DeviceType, DType
 
 __all__ = [
     "BaseSafeTensorsFileLoader", "Device", "DeviceType", "DType", "FilesBufferOnDevice",
-    "SafeTensorsFileLoader", "SafeTensorsMetadata", "SingleGroup", "TensorFrame",
+    "ParallelLoader", "PipelineParallel", "SafeTensorsFileLoader", "SafeTensorsMetadata", "SingleGroup", "TensorFrame",
     "fastsafe_open", "get_device_numa_node",
 ]

@@ -47,6 +47,17 @@ class FilesBufferOnDevice:
                 loader.free_dev_ptrs()
         self.rank_loaders = {}
 
+    def replicate_all(self) -> None:
+        """Give every rank every file image of this batch: one broadcast per file, after which
+        ``get_tensor`` returns views without further collectives.  This is the bulk form of
+        "``get_tensor`` for every key", the access pattern of vLLM's loader and of
+        ``PipelineParallel``.  Collective: all ranks call it at the same point."""
+        if self.pg.size() == 1:
+            return
+        for rank in sorted(self.rank_loaders):
+            for loader in self.rank_loaders[rank]:
+                loader.replicate(self.pg)
+
     def get_filename(self, tensor_name: str) -> str:
         if tensor_name not in self.key_to_rank_lidx:
             return ""

@@ -46,6 +46,8 @@ class LazyTensorFactory:
         self.lidx = lidx                    # 1-based index of the file among all files
         self.next_tag = 1
         self.disable_cache = disable_cache
+        self.replicated = False             # every rank holds the image (see replicate)
+        self.converted = False              # tensors were narrowed in place at load time
 
     # ---------------------------------------------------------------- file -> image
     def submit_io(self, use_buf_register: bool, max_copy_block_size: int) -> None:
@@ -56,6 +58,7 @@ class LazyTensorFactory:
     def wait_io(self, dtype: DType = DType.AUTO, noalign: bool = False) -> None:
         if self.copier is not None and self.gbuf is not None:
             self.tensors = self.copier.wait_io(self.gbuf, dtype=dtype, noalign=noalign)
+            self.converted = dtype != DType.AUTO
             self.copier = None
 
     def free_dev_ptrs(self) -> None:
@@ -64,6 +67,28 @@ class LazyTensorFactory:
             logger.debug("free_dev_ptrs: delete buf, addr=0x%x", self.gbuf.get_base_address())
             self.framework.free_tensor_memory(self.gbuf, self.device)
             self.gbuf = None
+
+    def replicate(self, pg: ProcessGroupBase) -> bool:
+        """Broadcast the whole file image from its owner so that every rank can instantiate every
+        tensor of the file as a view: one collective per file instead of one per tensor.
+        Collective: every rank must call it, in the same file order.  Returns False (and does
+        nothing) when the image cannot be shared as it is."""
+        if pg.size() == 1 or self.replicated:
+            return True
+        if self.converted:   # in-place narrowing changed the owner's layout only
+            return False
+        owner = self.rank == pg.rank()
+        total = self.metadata.size_bytes - self.metadata.header_length
+        if owner and self.gbuf is None:
+            raise Exception(f"replicate: the image of {self.metadata.src} was already released")
+        if not owner:
+            self.gbuf = self.framework.alloc_tensor_memory(total, self.device)
+        if total:
+            pg.broadcast(TorchTensor(self.device, DType.U8, self.gbuf.owner[:total]), self.rank)
+        if not owner:
+            self.tensors = self.metadata.get_tensors(self.gbuf, self.device, self.metadata.header_length)
+        self.replicated = True
+        return True
 
     # ---------------------------------------------------------------- helpers
     def _owned(self, what: str, tensor_name: str) -> TensorBase:
@@ -128,6 +153,8 @@ class LazyTensorFactory:
             return self.shuffled[tensor_name].clone().detach()
         frame = self.metadata.tensors[tensor_name]
         owner = self.rank == pg.rank()
+        if dim == -1 and self.replicated:
+            return self._owned("shuffle", tensor_name)   # view of this rank's copy of the image
         if dim == -1:
             if owner:
                 dst = self._owned("shuffle", tensor_name).clone().detach()

@@ -1,0 +1,107 @@
+"""PipelineParallel / ParallelLoader: the producer-consumer iterator (upstream
+parallel_loader.py:126-505) on CPU, one rank and two gloo ranks, against the oracle."""
+
+import json
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import fastsafetensors_b200 as fst
+from fastsafetensors_b200 import cpp
+from fastsafetensors_b200.frameworks import get_framework_op
+from oracle import st_oracle
+from tests.golden import cases
+from tests.helpers import digest_bytes, digest_tensor
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CASE = [c for c in cases.CASES if c["id"] == "llama3_70b_w8"][0]   # 30 small files
+
+
+def _expected(paths):
+    want = {}
+    for p in paths:
+        fo = st_oracle.FileOracle(p)
+        for n, e in fo.tensors.items():
+            want[n] = (list(e["shape"]), digest_bytes(fo.raw(n)))
+    return want
+
+
+@pytest.mark.parametrize("queue_size", [-1, 0, 2])
+def test_single_rank_yields_every_tensor_once(queue_size, case_files, leak_check):
+    paths = sorted(case_files(CASE))
+    want = _expected(paths)
+    it = fst.ParallelLoader(None, paths, queue_size=queue_size, use_tqdm_on_load=False, device="cpu",
+                            nogds=True, max_threads=2, slot_kb=64)
+    got = {}
+    for key, t in it.iterate_weights():
+        assert key not in got
+        got[key] = (list(t.shape), digest_tensor(t))
+    it.close()
+    assert got == want
+
+
+def test_order_follows_files_then_keys(case_files, leak_check):
+    paths = sorted(case_files(CASE))[:3]
+    it = fst.ParallelLoader(None, paths, use_tqdm_on_load=False, device="cpu", nogds=True)
+    keys = [k for k, _ in it.iterate_weights()]
+    it.close()
+    want = []
+    for p in paths:   # one rank: one file per batch, keys in data-offset order
+        want += list(st_oracle.FileOracle(p).tensors)
+    assert keys == want
+
+
+def test_producer_error_reaches_the_consumer(case_files, tmp_path, leak_check):
+    paths = sorted(case_files(CASE))[:2] + [str(tmp_path / "missing.safetensors")]
+    it = fst.ParallelLoader(None, paths, use_tqdm_on_load=False, device="cpu", nogds=True)
+    seen = 0
+    with pytest.raises(Exception):
+        for _ in it.iterate_weights():
+            seen += 1
+    it.close()
+    assert seen > 0
+
+
+def test_consumer_may_stop_early(case_files, leak_check):
+    paths = sorted(case_files(CASE))
+    it = fst.ParallelLoader(None, paths, queue_size=2, use_tqdm_on_load=False, device="cpu", nogds=True)
+    gen = it.iterate_weights()
+    next(gen)
+    gen.close()            # runs the generator's cleanup: producer stops, queued batches are freed
+    it.close()
+
+
+def test_only_one_producer_is_supported(case_files):
+    with pytest.raises(ValueError):
+        fst.ParallelLoader(None, case_files(CASE), max_concurrent_producers=2, device="cpu", nogds=True)
+
+
+def _rank_main(rank, world, paths, port, out_dir, queue_size):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    it = fst.ParallelLoader(dist.group.WORLD, paths, queue_size=queue_size, use_tqdm_on_load=False,
+                            device="cpu", nogds=True, max_threads=2, slot_kb=64)
+    got = {}
+    for key, t in it.iterate_weights():
+        got[key] = (list(t.shape), digest_tensor(t))
+    it.close()
+    assert get_framework_op("pytorch").get_mem_used() == 0
+    assert cpp.get_cpp_metrics().bounce_buffer_bytes == 0
+    with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
+        json.dump(got, f)
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("queue_size", [0, 1])
+def test_two_ranks_every_rank_gets_every_tensor(queue_size, case_files, tmp_path):
+    paths = sorted(case_files(CASE))[:7]          # odd count: the last batch has one file only
+    want = {k: list(v) for k, v in _expected(paths).items()}
+    mp.spawn(_rank_main, args=(2, paths, 29950 + queue_size, str(tmp_path), queue_size), nprocs=2, join=True)
+    for rank in range(2):
+        got = json.load(open(tmp_path / f"rank{rank}.json"))
+        assert got == want, rank

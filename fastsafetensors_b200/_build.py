@@ -1,6 +1,6 @@
 """Builds ``libfst_b200.so`` in-tree with nvcc for sm_100a.
 
-``python fastsafetensors_b200/_build.py`` (or ``build_native()``) compiles the three sources in
+``python fastsafetensors_b200/_build.py`` (or ``build_native()``) compiles the sources in
 ``csrc/`` into ``fastsafetensors_b200/libfst_b200.so``.  The build is skipped when the library
 is newer than every source and header.  nvcc cross-compiles without a GPU, so this also runs on
 a machine that has none.
@@ -18,7 +18,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC_DIR = os.path.join(PKG_DIR, "csrc")
 INCLUDE_DIR = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libfst_b200.so")
-SOURCES = ["fst_kernels.cu", "fst_reader.cu", "fst_host.cu"]
+SOURCES = ["fst_kernels.cu", "fst_reader.cu", "fst_host.cu", "fst_peer.cu"]
 
 
 def _nvcc() -> str:

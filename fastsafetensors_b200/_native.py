@@ -33,6 +33,7 @@ OK, EINVAL, ERANGE, ENOCUDA, ECUDA, EIO, ETIMEOUT, ENOMEM, ELIMIT, EGDS = (
 IO_AUTO, IO_DIRECT, IO_BUFFERED = 0, 1, 2
 GATHER_INLINE_OPS = 48
 GATHER_STATIC_MAX_OPS = 4096
+ARENA_HANDLE_BYTES = 64
 
 # every symbol the header declares; tests check that the library exports each one
 EXPORTS = (
@@ -41,7 +42,8 @@ EXPORTS = (
     "fst_host_free", "fst_read_host", "fst_io_alignment", "fst_get_metrics",
     "fst_reader_create", "fst_reader_submit", "fst_reader_wait", "fst_reader_destroy",
     "fst_reader_inject_fault", "fst_gather", "fst_gather_static", "fst_gather_host",
-    "fst_realign", "fst_release_workspaces",
+    "fst_realign", "fst_release_workspaces", "fst_arena_create", "fst_arena_export",
+    "fst_arena_open_peer", "fst_arena_close_peer", "fst_arena_destroy",
 )
 
 
@@ -130,6 +132,11 @@ def _load() -> ctypes.CDLL:
     lib.fst_gather_host.argtypes = [POINTER(Copy2D), c_uint64, c_int]
     lib.fst_realign.argtypes = [c_uint64, c_uint64, c_uint64, c_uint64]
     lib.fst_release_workspaces.restype = c_int
+    lib.fst_arena_create.argtypes = [c_uint64, POINTER(c_uint64)]
+    lib.fst_arena_export.argtypes = [c_uint64, c_void_p, c_uint64]
+    lib.fst_arena_open_peer.argtypes = [c_void_p, c_uint64, POINTER(c_uint64)]
+    lib.fst_arena_close_peer.argtypes = [c_uint64]
+    lib.fst_arena_destroy.argtypes = [c_uint64]
     if lib.fst_abi_version() != ABI_VERSION:
         raise ImportError(
             f"{LIB_PATH} has ABI version {lib.fst_abi_version()}, this package needs {ABI_VERSION}; rebuild it"

@@ -223,3 +223,132 @@ class ShardExchange:
             base = sum(sizes[:dst])
             out.append({s.name: self._view(s, base + s.offset) for s in lay.slots[0][dst]})
         return out
+
+
+class PeerArena:
+    """This rank's receive arena (plain ``cudaMalloc``, exported over CUDA IPC) and the mappings
+    of every peer's arena.  Creating one is a collective (the handles are all-gathered)."""
+
+    def __init__(self, pg, nbytes: int, device):
+        import ctypes
+
+        import torch
+        import torch.distributed as dist
+
+        from . import _native as nat
+
+        self._nat = nat
+        self.nbytes = max(int(nbytes), 256)
+        self.device = device
+        self.rank, self.world = pg.rank(), pg.size()
+        addr = ctypes.c_uint64(0)
+        nat.check(nat.lib.fst_arena_create(self.nbytes, ctypes.byref(addr)), "fst_arena_create")
+        self.address = addr.value
+        handle = ctypes.create_string_buffer(nat.ARENA_HANDLE_BYTES)
+        nat.check(nat.lib.fst_arena_export(self.address, handle, nat.ARENA_HANDLE_BYTES), "fst_arena_export")
+        handles: List[Optional[bytes]] = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=pg.real_pg)
+        self.peer_base: List[int] = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.peer_base.append(self.address)
+                continue
+            p = ctypes.c_uint64(0)
+            buf = ctypes.create_string_buffer(h, nat.ARENA_HANDLE_BYTES)
+            nat.check(nat.lib.fst_arena_open_peer(buf, nat.ARENA_HANDLE_BYTES, ctypes.byref(p)),
+                      "fst_arena_open_peer")
+            self.peer_base.append(p.value)
+        self._peers_open = True
+        self._span = _ArenaSpan(self)
+
+    def close_peers(self) -> None:
+        if self._peers_open:
+            for r, p in enumerate(self.peer_base):
+                if r != self.rank:
+                    self._nat.lib.fst_arena_close_peer(p)
+            self._peers_open = False
+
+    def as_tensor(self):
+        """``torch.uint8`` view of the arena; the arena is freed when the last view dies."""
+        import torch
+
+        return torch.as_tensor(self._span, device=self.device.as_str())
+
+
+class _ArenaSpan:
+    """Owner object behind the tensor views of an arena (CUDA array interface)."""
+
+    def __init__(self, arena: PeerArena):
+        self._nat = arena._nat
+        self._address = arena.address
+        self.__cuda_array_interface__ = {
+            "shape": (arena.nbytes,), "typestr": "|u1", "data": (arena.address, False), "version": 2,
+        }
+
+    def __del__(self):
+        try:
+            self._nat.lib.fst_arena_destroy(self._address)
+        except Exception:
+            pass
+
+
+class PeerShardExchange(ShardExchange):
+    """``ShardExchange`` whose transport is the gather kernel itself: every rank's receive
+    buffer is a peer arena, and the owner's single gather launch stores each shard directly
+    into the arena of its destination rank (NVLink peer stores).  No send buffer, no
+    ``all_to_all``; one 8-byte all-reduce per run serves as the barrier that tells a rank its
+    peers' kernels are done."""
+
+    def __init__(self, fb, requests: "Dict[str, Action]", world: int, me: int):
+        import torch
+
+        from . import _native as nat
+
+        self.fb, self.world, self.me, self.local = fb, world, me, False
+        self.names = list(requests)
+        self.layout = BatchLayout(world)
+        self.frames = {}
+        src_addr: Dict[str, int] = {}
+        self.device = next(l.device for ls in fb.rank_loaders.values() for l in ls)
+        if self.device.is_cpu:
+            raise Exception("the peer transport needs CUDA devices")
+        for name in self.names:
+            rank, lidx = fb._get_rank_lidx(name)
+            loader = fb.rank_loaders[rank][lidx]
+            self.frames[name] = loader.metadata.tensors[name]
+            self.layout.add(name, self.frames[name], rank, requests[name])
+            if rank == me:
+                if name not in loader.tensors:
+                    raise Exception(f"exchange: tensor {name} was not found, released? lidx={loader.lidx}")
+                src_addr[name] = loader.tensors[name].data_ptr()
+        lay = self.layout
+        self.arena = PeerArena(fb.pg, lay.recv_total(me), self.device)
+        self.recv = self.arena.as_tensor()
+        self.send = None
+        # region [me -> d] lives in d's arena at the offset where d expects owner `me`
+        region = [self.arena.peer_base[d] + lay.recv_offset(d, me) for d in range(world)]
+        mine = {n: f for n, f in self.frames.items() if n in src_addr}
+        ops = lay.fill_ops(me, mine, src_addr, region) if mine else []
+        self.payload_bytes = sum(o[2] * o[3] for o in ops)
+        self.launches = [(nat.make_ops(ops), len(ops), 0, 0)] if ops else []
+        self._flag = torch.zeros(1, dtype=torch.int32, device=self.device.as_str())
+
+    def run(self) -> None:
+        import torch.distributed as dist
+
+        from . import _native as nat
+
+        stream = self.fb.framework.current_stream(self.device)
+        for arr, n, base, length in self.launches:
+            nat.check(nat.lib.fst_gather(arr, n, 0, 0, base, length, stream), "fst_gather")
+        dist.all_reduce(self._flag, group=self.fb.pg.real_pg)   # stream-ordered barrier
+
+    def finish(self) -> None:
+        """Unmap the peers' arenas; collective (ends in a barrier) so that no rank can free its
+        arena while a peer still has it mapped."""
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.current_stream().synchronize()
+        self.arena.close_peers()
+        dist.barrier(group=self.fb.pg.real_pg)

@@ -9,6 +9,7 @@ the same order (they end in collectives).
 
 from __future__ import annotations
 
+import os
 from collections import OrderedDict
 from typing import Any, Dict, List, Optional, Set, Tuple
 
@@ -149,8 +150,8 @@ class FilesBufferOnDevice:
         )
         return self.exchange(requests)
 
-    def exchange(self, requests: "OrderedDict[str, Tuple]",
-                 max_batch_bytes: int = 8 << 30) -> Dict[str, TensorBase]:
+    def exchange(self, requests: "OrderedDict[str, Tuple]", max_batch_bytes: int = 8 << 30,
+                 transport: Optional[str] = None) -> Dict[str, TensorBase]:
         """Serve many requests at once: ``{name: ("shard", dim) | ("replicate",) | ("push", r)}``.
 
         Per batch (requests are cut into batches of at most ``max_batch_bytes`` outgoing bytes
@@ -159,8 +160,13 @@ class FilesBufferOnDevice:
         a device synchronisation per tensor (tensor_factory.py:143,186).  Results are views of
         the batch's receive buffer.  For a pushed tensor only the destination rank gets an
         entry.  Every rank must pass the same requests in the same order.
+
+        ``transport``: ``"nccl"`` packs into a send buffer and exchanges with
+        ``all_to_all_single``; ``"peer"`` (CUDA devices of one machine) lets the gather kernel
+        store every shard straight into the destination rank's receive arena over NVLink.
+        Default: the ``FST_B200_TRANSPORT`` environment variable, else ``"nccl"``.
         """
-        from .batch import ShardExchange
+        from .batch import PeerShardExchange, ShardExchange
 
         world, me = self.pg.size(), self.pg.rank()
         out: Dict[str, TensorBase] = {}
@@ -169,9 +175,20 @@ class FilesBufferOnDevice:
                 rank, lidx = self._get_rank_lidx(name)
                 out[name] = self.rank_loaders[rank][lidx].tensors[name]
             return out
+        device = next(l.device for ls in self.rank_loaders.values() for l in ls)
+        if transport is None:
+            transport = os.environ.get("FST_B200_TRANSPORT", "nccl")
+        if transport not in ("nccl", "peer"):
+            raise ValueError(f"transport must be 'nccl' or 'peer', got {transport!r}")
         for names in self._batches(requests, world, max_batch_bytes):
-            ex = ShardExchange(self, OrderedDict((n, requests[n]) for n in names), world, me, local=False)
-            ex.run()
+            batch = OrderedDict((n, requests[n]) for n in names)
+            if transport == "peer" and not device.is_cpu:
+                ex = PeerShardExchange(self, batch, world, me)
+                ex.run()
+                ex.finish()
+            else:
+                ex = ShardExchange(self, batch, world, me, local=False)
+                ex.run()
             out.update(ex.results())
             for name in names:
                 self._mark(*self.key_to_rank_lidx[name], name)

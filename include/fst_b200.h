@@ -240,6 +240,30 @@ int fst_gather_host(const fst_copy2d_t *ops, uint64_t n_ops, int threads);
  * (copier/gds.py:138-159). */
 int fst_realign(uint64_t dst, uint64_t src, uint64_t nbytes, uint64_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Peer arenas: receive buffers that the other ranks of one machine can write into
+ *
+ * Replaces the transport half of LazyTensorFactory.shuffle / shuffle_multi_cols
+ * (tensor_factory.py:186,258 -> frameworks/_torch.py:151-178: one NCCL scatter and a device
+ * synchronisation per tensor).  Every rank creates an arena sized for what it will receive,
+ * exports a 64-byte handle, and opens the handles of its peers; the owner of a file then gives
+ * fst_gather destination addresses inside its peers' arenas, so the pack and the transfer are
+ * one kernel: shards leave the owner's HBM once and land in the consumer's HBM over NVLink.
+ * A barrier after the launch (any small collective on the same stream) tells a rank that all
+ * its peers' kernels have finished.  Importers must close their mapping before the exporter
+ * destroys the arena.
+ * ---------------------------------------------------------------------------------------- */
+#define FST_ARENA_HANDLE_BYTES 64
+
+/* cudaMalloc an arena of nbytes on the current device; *arena is its device address. */
+int fst_arena_create(uint64_t nbytes, uint64_t *arena);
+/* Write the arena's inter-process handle (FST_ARENA_HANDLE_BYTES) into handle. */
+int fst_arena_export(uint64_t arena, void *handle, uint64_t handle_bytes);
+/* Map a peer's arena into this process; *peer_addr is valid on the current device. */
+int fst_arena_open_peer(const void *handle, uint64_t handle_bytes, uint64_t *peer_addr);
+int fst_arena_close_peer(uint64_t peer_addr);
+int fst_arena_destroy(uint64_t arena);
+
 /* Free the per-device workspaces of fst_gather (they are also freed at process exit). */
 int fst_release_workspaces(void);
 

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 MULTI = [c for c in cases.CASES if c["world"] > 1]
 
 
-@pytest.mark.parametrize("batched", [False, True], ids=["per_tensor", "batched"])
+@pytest.mark.parametrize("batched", [False, "nccl", "peer"], ids=["per_tensor", "batched_nccl", "batched_peer"])
 @pytest.mark.parametrize("case", MULTI, ids=[c["id"] for c in MULTI])
 def test_nccl_ranks_match_upstream(case, batched, golden, case_files, tmp_path):
     world = case["world"]
@@ -23,8 +23,8 @@ def test_nccl_ranks_match_upstream(case, batched, golden, case_files, tmp_path):
     if batched and case["steps"][0][0] != "plan":
         pytest.skip("as_dict in the per-tensor run already goes through the batched exchange")
     paths = case_files(case)
-    port = 29900 + 2 * cases.CASES.index(case) + int(batched)
-    mp.spawn(_rank_main, args=(world, case, paths, port, str(tmp_path), batched, "nccl"),
+    port = 29900 + 3 * cases.CASES.index(case) + [False, "nccl", "peer"].index(batched)
+    mp.spawn(_rank_main, args=(world, case, paths, port, str(tmp_path), bool(batched), "nccl", batched or "nccl"),
              nprocs=world, join=True)
     for rank in range(world):
         got = json.load(open(tmp_path / f"rank{rank}.json"))

@@ -16,7 +16,7 @@ from tests.golden import cases
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _rank_main(rank, world, case, paths, port, out_dir, batched=False, backend="gloo"):
+def _rank_main(rank, world, case, paths, port, out_dir, batched=False, backend="gloo", transport="nccl"):
     sys.path.insert(0, ROOT)
     import fastsafetensors_b200 as fst
     from fastsafetensors_b200 import cpp
@@ -39,7 +39,7 @@ def _rank_main(rank, world, case, paths, port, out_dir, batched=False, backend="
         if step[0] == "plan" and batched:
             # the whole plan in one batched exchange (tiny batches force several rounds)
             plan = OrderedDict((n, (a[0], a[1] % world) if a[0] == "push" else a) for n, a in cases.plan(case))
-            got = fb.exchange(plan, max_batch_bytes=1 << 20)
+            got = fb.exchange(plan, max_batch_bytes=1 << 20, transport=transport)
             for name, action in plan.items():
                 if action[0] == "push" and action[1] != rank:
                     assert name not in got

@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    ap.add_argument("--impl", default="b200", choices=("b200", "reference", "reference-cuda"))
     ap.add_argument("--config", default=WORKLOAD)
     ap.add_argument("--scale", default="full", choices=("full", "tiny"))
     ap.add_argument("--dir", default=os.environ.get("FST_BENCH_DIR", "/tmp/fst_bench"))
@@ -366,6 +366,8 @@ def b200_arm(args) -> dict:
                 result["e2e"]["value"] / result["storage_read"]["cold_direct_gbs"], 3)
     if rank == 0 and not args.no_cpu_baseline and not args.kernel_only:
         result["cpu_baseline"] = cpu_baseline(spec, paths)
+        if world == 1:
+            result["reference_cuda_nogds"] = reference_cuda_subprocess(args)
     if world > 1:
         dist.destroy_process_group()
     return result if rank == 0 else {}
@@ -496,6 +498,18 @@ def cpu_baseline(spec, paths) -> dict:
             "warm_value": round(spec.data_bytes / warm / GB, 3)}
 
 
+def reference_cuda_subprocess(args) -> dict:
+    """Run ``--impl reference-cuda`` in a child process (its own CUDA context and allocator)."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference-cuda", "--config", args.config,
+           "--scale", args.scale, "--dir", args.dir, "--layers", str(args.layers)]
+    try:
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+        line = [l for l in proc.stdout.splitlines() if l.startswith("{")]
+        return json.loads(line[-1]) if line else {"unavailable": (proc.stderr or "no output")[-300:]}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {e}"}
+
+
 def reference_arm(args) -> dict:
     from fastsafetensors_b200 import synth
 
@@ -530,8 +544,43 @@ def reference_arm(args) -> dict:
     }
 
 
+def reference_cuda_arm(args) -> dict:
+    """Upstream's own CUDA path (nogds: buffered pread + synchronous cudaMemcpy per chunk) on
+    one GPU: files -> HBM, every tensor instantiated.  One rank cannot shard, so this times the
+    load only; it is reported beside the b200 arm, not as the reference arm."""
+    sys.path.insert(0, REF_DIR)
+    import torch
+
+    import fastsafetensors as ref
+    from fastsafetensors_b200 import synth
+
+    spec = load_spec(args)
+    paths = prepare_files(spec, args.dir, 0, lambda: None)
+    out = {}
+    for label, cold in (("cold", True), ("warm", False)):
+        if cold:
+            synth.drop_page_cache(paths)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        loader = ref.SafeTensorsFileLoader(ref.SingleGroup(), "cuda:0", nogds=True)
+        loader.add_filenames({0: paths})
+        fb = loader.copy_files_to_device()
+        keep = [fb.get_tensor(k) for k in fb.key_to_rank_lidx]
+        torch.cuda.synchronize()
+        out[label] = round(spec.data_bytes / (time.perf_counter() - t0) / GB, 3)
+        del keep
+        fb.close()
+        loader.close()
+    return {"impl": "reference-cuda", "unit": "GB/s", "cold": out["cold"], "warm": out["warm"],
+            "what": "upstream fastsafetensors 0.3.2, device cuda:0, nogds, one rank, library defaults; "
+                    "files -> HBM and get_tensor of every key (no sharding with one rank)"}
+
+
 def main() -> None:
     args = parse_args()
+    if args.impl == "reference-cuda":
+        print(json.dumps(reference_cuda_arm(args)), flush=True)
+        return
     out = reference_arm(args) if args.impl == "reference" else b200_arm(args)
     if out:
         print(json.dumps(out), flush=True)

@@ -43,7 +43,7 @@ EXPORTS = (
     "fst_reader_create", "fst_reader_submit", "fst_reader_wait", "fst_reader_destroy",
     "fst_reader_inject_fault", "fst_gather", "fst_gather_static", "fst_gather_host",
     "fst_realign", "fst_release_workspaces", "fst_arena_create", "fst_arena_export",
-    "fst_arena_open_peer", "fst_arena_close_peer", "fst_arena_destroy",
+    "fst_arena_open_peer", "fst_arena_close_peer", "fst_arena_destroy", "fst_convert",
 )
 
 
@@ -86,6 +86,19 @@ class Copy2D(Structure):
         ("src_pitch", c_uint64),
         ("dst_pitch", c_uint64),
     ]
+
+
+class ConvertOp(Structure):
+    _fields_ = [
+        ("src", c_uint64),
+        ("dst", c_uint64),
+        ("n_elements", c_uint64),
+        ("src_dtype", c_int32),
+        ("dst_dtype", c_int32),
+    ]
+
+
+DT_CODES = {"F64": 0, "F32": 1, "F16": 2, "BF16": 3}
 
 
 class NativeError(RuntimeError):
@@ -132,6 +145,7 @@ def _load() -> ctypes.CDLL:
     lib.fst_gather_host.argtypes = [POINTER(Copy2D), c_uint64, c_int]
     lib.fst_realign.argtypes = [c_uint64, c_uint64, c_uint64, c_uint64]
     lib.fst_release_workspaces.restype = c_int
+    lib.fst_convert.argtypes = [POINTER(ConvertOp), c_uint64, c_uint64]
     lib.fst_arena_create.argtypes = [c_uint64, POINTER(c_uint64)]
     lib.fst_arena_export.argtypes = [c_uint64, c_void_p, c_uint64]
     lib.fst_arena_open_peer.argtypes = [c_void_p, c_uint64, POINTER(c_uint64)]
@@ -211,6 +225,17 @@ def gather_host(ops: Sequence[Tuple[int, int, int, int, int, int]], threads: int
         return
     arr = make_ops(ops)
     check(lib.fst_gather_host(arr, len(ops), threads), "fst_gather_host")
+
+
+def convert(ops: Sequence[Tuple[int, int, int, int, int]], stream: int) -> None:
+    """``fst_convert``: (src, dst, n_elements, src_code, dst_code) tuples, one launch."""
+    if not ops:
+        return
+    arr = (ConvertOp * len(ops))()
+    for i, o in enumerate(ops):
+        a = arr[i]
+        a.src, a.dst, a.n_elements, a.src_dtype, a.dst_dtype = o
+    check(lib.fst_convert(arr, len(ops), stream), "fst_convert")
 
 
 def realign(dst: int, src: int, nbytes: int, stream: int) -> None:

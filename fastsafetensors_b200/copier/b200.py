@@ -60,7 +60,59 @@ class B200FileCopier(CopierInterface):
                 self.reader.wait(request)
             except nat.NativeError as e:
                 raise Exception(f"wait_io: read of {self.metadata.src} failed: {e}") from e
+        if dtype != DType.AUTO and self.device.type != DeviceType.CPU:
+            tensors = self.metadata.get_tensors(gbuf, self.device, self.metadata.header_length)
+            return self._convert_on_device(gbuf, tensors, dtype)
         return self.metadata.get_tensors(gbuf, self.device, self.metadata.header_length, dtype=dtype)
+
+    def _convert_on_device(self, gbuf: gds_device_buffer, tensors: Dict[str, Any], dtype: DType) -> Dict[str, Any]:
+        """Load-time narrowing (upstream common.py:355-375) on a CUDA image: every tensor is
+        converted out of place into a new, compact image by ONE launch of the convert kernel
+        (plus one gather launch for tensors that already have the target type); pairs the kernel
+        does not know go through ``torch.Tensor.to`` as upstream's all do.  The old image is
+        released and ``gbuf`` takes over the new one."""
+        import torch
+
+        from ..frameworks._torch import TorchTensor, dtype_convert
+
+        meta = self.metadata
+        for name, frame in meta.tensors.items():
+            if dtype.bits > frame.dtype.bits:
+                raise Exception(
+                    f"Online type conversion to larger sizes is not supported ({frame.dtype} -> {dtype})")
+        offsets: Dict[str, int] = {}
+        total = 0
+        for name, frame in meta.tensors.items():
+            offsets[name] = total
+            count = 1
+            for extent in frame.shape:
+                count *= extent
+            total += (count * dtype.bits // 8 + 15) // 16 * 16
+        new = self.framework.alloc_tensor_memory(total, self.device)
+        image = new.owner
+        stream = self.framework.current_stream(self.device)
+        convert_ops, copy_ops = [], []
+        out: Dict[str, Any] = {}
+        for name, frame in meta.tensors.items():
+            src = tensors[name].get_raw()
+            count = src.numel()
+            nbytes = count * dtype.bits // 8
+            view = image[offsets[name]: offsets[name] + nbytes].view(dtype_convert[dtype]).reshape(frame.shape)
+            s_code, d_code = nat.DT_CODES.get(frame.dtype.value), nat.DT_CODES.get(dtype.value)
+            if frame.dtype == dtype:
+                copy_ops.append((src.data_ptr(), view.data_ptr(), 1, nbytes, 0, 0))
+            elif s_code is not None and d_code is not None and d_code != 0:
+                convert_ops.append((src.data_ptr(), view.data_ptr(), count, s_code, d_code))
+            elif count:
+                view.copy_(src.to(dtype=dtype_convert[dtype]))
+            frame.dtype = dtype
+            out[name] = TorchTensor(self.device, dtype, view)
+        nat.convert(convert_ops, stream)
+        nat.gather(copy_ops, stream)
+        tensors.clear()
+        self.framework.free_tensor_memory(gbuf, self.device)   # the launches above are ordered
+        gbuf.adopt(new)                                        # before any reuse of that memory
+        return out
 
 
 def new_b200_file_copier(device: Device, bbuf_size_kb: int = 16 * 1024, max_threads: int = 16,

@@ -49,6 +49,12 @@ class gds_device_buffer:
         """Drop the reference to the owning allocation (views of it keep it alive)."""
         self._owner = None
 
+    def adopt(self, other: "gds_device_buffer") -> None:
+        """Become ``other`` (address, length, owner); ``other`` is emptied."""
+        self._base, self._length, self._use_cuda, self._owner = (
+            other._base, other._length, other._use_cuda, other._owner)
+        other._owner = None
+
     def check_range(self, offset: int, length: int) -> int:
         if offset < 0 or length < 0 or offset + length > self._length:
             raise IndexError(

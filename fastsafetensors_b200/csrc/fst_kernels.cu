@@ -672,3 +672,191 @@ extern "C" int fst_gather_static(const fst_copy2d_t *ops, uint64_t n_ops, uint64
     g_counters.bytes_gathered.fetch_add(payload, std::memory_order_relaxed);
     return FST_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// fst_convert: narrowing floating-point conversion of many tensors in one launch
+// ------------------------------------------------------------------------------------------
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace fst {
+
+// Device record of one conversion (64 bytes, so that it can share the gather's op-table ring).
+struct ConvertOp {
+    uint64_t src;
+    uint64_t dst;
+    uint64_t n;            // elements
+    uint64_t first_chunk;  // chunks of CONVERT_CHUNK elements in earlier ops
+    uint32_t src_t;
+    uint32_t dst_t;
+    uint64_t pad[3];
+};
+static_assert(sizeof(ConvertOp) == sizeof(GatherOp), "ConvertOp shares the GatherOp table ring");
+
+constexpr unsigned CONVERT_CHUNK = 4096;  // elements one warp converts per step (128 per lane)
+
+__device__ __forceinline__ float load_as_float(const void *p, uint32_t t, uint64_t i) {
+    switch (t) {
+        case FST_DT_F64: return (float)reinterpret_cast<const double *>(p)[i];
+        case FST_DT_F32: return reinterpret_cast<const float *>(p)[i];
+        case FST_DT_F16: return __half2float(reinterpret_cast<const __half *>(p)[i]);
+        default: return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
+    }
+}
+
+__device__ __forceinline__ void store_from_float(void *p, uint32_t t, uint64_t i, float v) {
+    switch (t) {
+        case FST_DT_F32: reinterpret_cast<float *>(p)[i] = v; break;
+        case FST_DT_F16: reinterpret_cast<__half *>(p)[i] = __float2half_rn(v); break;
+        default: reinterpret_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v); break;
+    }
+}
+
+// One warp per chunk; lanes take interleaved groups of 4 elements so that a warp instruction
+// touches one contiguous run.  F32 -> 16-bit with aligned addresses moves 16-byte loads and
+// 8-byte stores; every other case goes element by element (still coalesced).
+__global__ void __launch_bounds__(CTA_THREADS)
+fst_convert_kernel(const ConvertOp *__restrict__ ops, unsigned n_ops, uint64_t total_chunks) {
+    const unsigned lane = threadIdx.x & 31u;
+    const uint64_t warp = (uint64_t)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
+    const uint64_t step = (uint64_t)gridDim.x * WARPS_PER_CTA;
+    for (uint64_t c = warp; c < total_chunks; c += step) {
+        unsigned lo = 0, hi = n_ops;
+        while (hi - lo > 1) {
+            const unsigned mid = (lo + hi) >> 1;
+            if (ops[mid].first_chunk <= c) lo = mid; else hi = mid;
+        }
+        const ConvertOp &op = ops[lo];
+        const uint64_t beg = (c - op.first_chunk) * CONVERT_CHUNK;
+        const uint64_t end = beg + CONVERT_CHUNK < op.n ? beg + CONVERT_CHUNK : op.n;
+        const void *s = reinterpret_cast<const void *>(op.src);
+        void *d = reinterpret_cast<void *>(op.dst);
+        const bool fast = op.src_t == FST_DT_F32 && (op.dst_t == FST_DT_F16 || op.dst_t == FST_DT_BF16) &&
+                          ((op.src & 15u) == 0) && ((op.dst & 7u) == 0);
+        if (fast) {
+            const float4 *s4 = reinterpret_cast<const float4 *>(s);
+            uint2 *d4 = reinterpret_cast<uint2 *>(d);
+            const uint64_t g_end = end >> 2;
+            for (uint64_t g = (beg >> 2) + lane; g < g_end; g += 32) {
+                const float4 v = __ldcs(s4 + g);
+                uint2 o;
+                if (op.dst_t == FST_DT_F16) {
+                    const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+                    o.x = *reinterpret_cast<const unsigned *>(&a);
+                    o.y = *reinterpret_cast<const unsigned *>(&b);
+                } else {
+                    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+                    o.x = *reinterpret_cast<const unsigned *>(&a);
+                    o.y = *reinterpret_cast<const unsigned *>(&b);
+                }
+                __stcs(d4 + g, o);
+            }
+            for (uint64_t i = (g_end << 2) + lane; i < end; i += 32)   // ragged tail of the tensor
+                store_from_float(d, op.dst_t, i, load_as_float(s, op.src_t, i));
+        } else {
+            for (uint64_t i = beg + lane; i < end; i += 32)
+                store_from_float(d, op.dst_t, i, load_as_float(s, op.src_t, i));
+        }
+    }
+}
+
+}  // namespace fst
+
+extern "C" int fst_convert(const fst_convert_op_t *ops, uint64_t n_ops, uint64_t stream) {
+    using namespace fst;
+    clear_error();
+    if (!cuda_usable()) {
+        set_error("fst_convert: no CUDA device");
+        return FST_ENOCUDA;
+    }
+    if (n_ops == 0) return FST_OK;
+    if (ops == nullptr) {
+        set_error("fst_convert: ops is null");
+        return FST_EINVAL;
+    }
+    static const unsigned width[4] = {8, 4, 2, 2};
+    std::vector<ConvertOp> recs;
+    recs.reserve(n_ops);
+    uint64_t chunks = 0;
+    for (uint64_t i = 0; i < n_ops; ++i) {
+        const fst_convert_op_t &c = ops[i];
+        if (c.n_elements == 0) continue;
+        if (c.src == 0 || c.dst == 0 || c.src_dtype < 0 || c.src_dtype > 3 || c.dst_dtype < 1 ||
+            c.dst_dtype > 3) {
+            set_error("fst_convert: op %llu: bad address or dtype code", (unsigned long long)i);
+            return FST_EINVAL;
+        }
+        if (width[c.dst_dtype] > width[c.src_dtype]) {
+            set_error("fst_convert: op %llu widens (%d -> %d); only narrowing or same-width "
+                      "conversions are supported", (unsigned long long)i, c.src_dtype, c.dst_dtype);
+            return FST_EINVAL;
+        }
+        if (c.src % width[c.src_dtype] || c.dst % width[c.dst_dtype]) {
+            set_error("fst_convert: op %llu: address not aligned to its element size",
+                      (unsigned long long)i);
+            return FST_EINVAL;
+        }
+        const uint64_t s_end = c.src + c.n_elements * width[c.src_dtype];
+        const uint64_t d_end = c.dst + c.n_elements * width[c.dst_dtype];
+        if (c.dst < s_end && c.src < d_end) {
+            set_error("fst_convert: op %llu: source and destination overlap", (unsigned long long)i);
+            return FST_EINVAL;
+        }
+        ConvertOp r = {};
+        r.src = c.src;
+        r.dst = c.dst;
+        r.n = c.n_elements;
+        r.src_t = (uint32_t)c.src_dtype;
+        r.dst_t = (uint32_t)c.dst_dtype;
+        r.first_chunk = chunks;
+        chunks += (c.n_elements + CONVERT_CHUNK - 1) / CONVERT_CHUNK;
+        recs.push_back(r);
+    }
+    if (recs.empty()) return FST_OK;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= MAX_DEVICES) {
+        set_error("fst_convert: device index %d not supported", dev);
+        return FST_ELIMIT;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    int rc = ensure_workspace(dev);
+    if (rc != FST_OK) return rc;
+    const int limit = grid_limit_for(dev);
+    Workspace &w = g_ws[dev];
+    size_t pos = 0;
+    while (pos < recs.size()) {
+        const size_t take = std::min<size_t>(recs.size() - pos, TABLE_SLOT_OPS);
+        const int slot = w.next;
+        w.next = (w.next + 1) % TABLE_SLOTS;
+        cudaError_t e = cudaEventSynchronize(w.done[slot]);
+        ConvertOp *host = reinterpret_cast<ConvertOp *>(w.host_tab[slot]);
+        const uint64_t base = recs[pos].first_chunk;
+        uint64_t n_chunks = 0;
+        for (size_t i = 0; i < take; ++i) {
+            host[i] = recs[pos + i];
+            host[i].first_chunk -= base;
+            n_chunks += (recs[pos + i].n + CONVERT_CHUNK - 1) / CONVERT_CHUNK;
+        }
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(w.dev_tab[slot], host, take * sizeof(ConvertOp), cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) {
+            set_error("fst_convert: op table upload failed: %s", cudaGetErrorString(e));
+            return FST_ECUDA;
+        }
+        uint64_t want = (n_chunks + WARPS_PER_CTA - 1) / WARPS_PER_CTA;
+        if (want > (uint64_t)limit) want = (uint64_t)limit;
+        fst_convert_kernel<<<(unsigned)want, CTA_THREADS, 0, st>>>(
+            reinterpret_cast<const ConvertOp *>(w.dev_tab[slot]), (unsigned)take, n_chunks);
+        cudaEventRecord(w.done[slot], st);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            set_error("fst_convert: launch failed: %s", cudaGetErrorString(e));
+            return FST_ECUDA;
+        }
+        g_counters.kernel_launches.fetch_add(1, std::memory_order_relaxed);
+        pos += take;
+    }
+    return FST_OK;
+}

@@ -240,6 +240,25 @@ int fst_gather_host(const fst_copy2d_t *ops, uint64_t n_ops, int threads);
  * (copier/gds.py:138-159). */
 int fst_realign(uint64_t dst, uint64_t src, uint64_t nbytes, uint64_t stream);
 
+/* Narrowing conversion at load time: many tensors in ONE launch, out of place.
+ * Replaces the per-tensor `t.to(dtype)` + `copy_` of SafeTensorsMetadata.get_tensors
+ * (common.py:355-375, two torch kernels and a temporary per tensor).  Floating-point types
+ * only; the destination must not be wider than the source; rounding is round-to-nearest-even
+ * through float (what `torch.Tensor.to` does on a CUDA device); ranges must not overlap and
+ * addresses must be aligned to their element size. */
+#define FST_DT_F64 0
+#define FST_DT_F32 1
+#define FST_DT_F16 2
+#define FST_DT_BF16 3
+typedef struct fst_convert_op {
+    uint64_t src;
+    uint64_t dst;
+    uint64_t n_elements;
+    int32_t src_dtype; /* FST_DT_* */
+    int32_t dst_dtype; /* FST_DT_F32, FST_DT_F16 or FST_DT_BF16 */
+} fst_convert_op_t;
+int fst_convert(const fst_convert_op_t *ops, uint64_t n_ops, uint64_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Peer arenas: receive buffers that the other ranks of one machine can write into
  *

@@ -189,3 +189,61 @@ def test_full_size_tensors_by_properties():
     got0 = packed[: shard_bytes].view(torch.int16).reshape(4096, -1)[:64].cpu().numpy().view(np.uint8).reshape(-1)
     want0, _ = st_oracle.shard(raw, (64, 14336), "BF16", 1, 0, world)
     assert np.array_equal(got0, want0)
+
+
+# ------------------------------------------------------------------ load-time narrowing
+def test_convert_kernel_matches_torch_bit_for_bit():
+    """fst_convert against torch.Tensor.to on the same device, including ties, denormals,
+    infinities and values that overflow the target."""
+    g = torch.Generator(device=DEV).manual_seed(9)
+    n = (1 << 20) + 37
+    base = torch.randn(n, device=DEV, generator=g) * 3.0
+    special = torch.tensor([0.0, -0.0, 1.0, 65504.0, 65520.0, 1e-8, -1e-8, 3.3895e38, float("inf"),
+                            -float("inf"), 1.00390625, 1.001953125, 2.0 ** -24, 2.0 ** -25, 1e30],
+                           device=DEV)
+    src32 = torch.cat([base, special, base * 1e-6, base * 1e6])
+    stream = int(torch.cuda.current_stream().cuda_stream)
+    cases_ = [(src32, "F32", torch.float16, "F16"), (src32, "F32", torch.bfloat16, "BF16"),
+              (src32.double() * 1.0000001, "F64", torch.float32, "F32"),
+              (src32.double(), "F64", torch.bfloat16, "BF16"), (src32.double(), "F64", torch.float16, "F16"),
+              (src32.half(), "F16", torch.bfloat16, "BF16"), (src32.bfloat16(), "BF16", torch.float16, "F16")]
+    for src, s_name, dst_t, d_name in cases_:
+        for shift in (0, 1):          # shift 1 element: the unaligned (element-wise) path
+            s = src[shift:]
+            want = s.to(dst_t)
+            got = torch.empty(s.numel() + 8, dtype=dst_t, device=DEV)[shift: shift + s.numel()]
+            nat.convert([(s.data_ptr(), got.data_ptr(), s.numel(), nat.DT_CODES[s_name], nat.DT_CODES[d_name])], stream)
+            torch.cuda.synchronize()
+            a = got.view(torch.int16 if dst_t != torch.float32 else torch.int32)
+            b = want.view(a.dtype)
+            assert torch.equal(a, b), (s_name, d_name, shift)
+    with pytest.raises(nat.NativeError):
+        nat.convert([(src32.data_ptr(), src32.data_ptr() + 4, 10, 1, 3)], stream)       # overlap
+    with pytest.raises(nat.NativeError):
+        nat.convert([(src32.data_ptr(), base.data_ptr(), 10, 2, 1)], stream)            # widening
+
+
+def test_loader_narrowing_on_cuda_matches_torch(tmp_path, leak_check):
+    from safetensors.torch import save_file
+
+    from fastsafetensors_b200.st_types import DType
+
+    torch.manual_seed(1)
+    t = {"w": torch.randn(300, 257), "v": torch.randn(5), "h": torch.randn(64, 64).half(),
+         "b": torch.randn(33, 3).bfloat16(), "i": torch.randint(-100, 100, (7, 9), dtype=torch.int32)}
+    p = str(tmp_path / "mixed.safetensors")
+    save_file(t, p)
+    loader = fst.SafeTensorsFileLoader(None, DEV, nogds=True)
+    loader.add_filenames({0: [p]})
+    fb = loader.copy_files_to_device(dtype=DType.BF16)
+    for k, ref in t.items():
+        got = fb.get_tensor(k)
+        assert got.dtype == torch.bfloat16 and got.is_cuda
+        assert torch.equal(got.cpu().view(torch.int16), ref.to(DEV).to(torch.bfloat16).cpu().view(torch.int16)), k
+    fb.close()
+    loader.close()
+    loader = fst.SafeTensorsFileLoader(None, DEV, nogds=True)
+    loader.add_filenames({0: [p]})
+    with pytest.raises(Exception, match="larger sizes"):
+        loader.copy_files_to_device(dtype=DType.F64)
+    loader.close()

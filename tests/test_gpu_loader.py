@@ -170,25 +170,35 @@ def test_owner_packing_for_all_ranks_matches_upstream(case, golden, case_files, 
     loader.close()
 
 
-def test_full_size_tensors_by_properties():
-    """Llama-3-8B sized tensors (too big for the golden file): a dim-1 shard pack must be a
-    permutation that preserves the multiset of 8-byte words per row block, and the oracle on a
-    sample of rows must agree bit for bit."""
-    shape, world, bits = (4096, 14336), 8, 16
+@pytest.mark.parametrize("shape,dim,world", [
+    ((4096, 14336), 1, 8),     # Llama-3-8B down_proj
+    ((14336, 4096), 0, 8),     # Llama-3-8B gate/up
+    ((8192, 28672), 1, 8),     # Llama-3-70B down_proj, 7 KiB segments at 56 KiB pitch
+    ((8192, 8192), 1, 8),      # Llama-3-70B o_proj, 2 KiB segments
+    ((128256, 8192), 0, 8),    # Llama-3-70B embed_tokens / lm_head, 2.1 GB
+    ((5120, 13824), 1, 4),     # Llama-2-13B down_proj (fp16)
+    ((4096, 14336), 1, 1),     # Mixtral w2 pushed whole
+])
+def test_full_size_tensors_by_properties(shape, dim, world):
+    """Tensors at the benchmark configurations' real sizes (too big for the golden file): the
+    pack must equal ``torch.chunk`` of the same tensor bit for bit, preserve the checksum of
+    checksums, and agree with the oracle on a sample of rows."""
+    bits = 16
     g = torch.Generator(device=DEV).manual_seed(5)
     t = torch.randint(0, 1 << 15, shape, dtype=torch.int16, device=DEV, generator=g)
     n = t.numel() * 2
-    ops, shard_bytes = shard_plan.scatter_ops(t.data_ptr(), 0, shape, bits, 1, world)
+    ops, shard_bytes = shard_plan.scatter_ops(t.data_ptr(), 0, shape, bits, dim, world)
     packed = torch.empty(n, dtype=torch.uint8, device=DEV)
     nat.gather([(o[0], o[1] + packed.data_ptr()) + o[2:] for o in ops],
                int(torch.cuda.current_stream().cuda_stream), (t.data_ptr(), n), (packed.data_ptr(), n))
     assert int(packed.view(torch.int64).sum()) == int(t.view(torch.int64).sum())  # checksum of checksums
-    want = torch.cat([c.contiguous().reshape(-1) for c in t.chunk(world, dim=1)])
+    want = torch.cat([c.contiguous().reshape(-1) for c in t.chunk(world, dim=dim)])
     assert torch.equal(packed.view(torch.int16), want)
-    raw = t[:64].cpu().numpy().view(np.uint8).reshape(-1)
-    got0 = packed[: shard_bytes].view(torch.int16).reshape(4096, -1)[:64].cpu().numpy().view(np.uint8).reshape(-1)
-    want0, _ = st_oracle.shard(raw, (64, 14336), "BF16", 1, 0, world)
-    assert np.array_equal(got0, want0)
+    if dim == 1:
+        raw = t[:64].cpu().numpy().view(np.uint8).reshape(-1)
+        got0 = packed[: shard_bytes].view(torch.int16).reshape(shape[0], -1)[:64].cpu().numpy().view(np.uint8).reshape(-1)
+        want0, _ = st_oracle.shard(raw, (64, shape[1]), "BF16", 1, 0, world)
+        assert np.array_equal(got0, want0)
 
 
 # ------------------------------------------------------------------ load-time narrowing

@@ -207,7 +207,13 @@ def b200_arm(args) -> dict:
     def make_exchange(fb) -> ShardExchange:
         return ShardExchange(fb, plan, tp, rank if world > 1 else 0, local=(world == 1))
 
+    def note(msg: str) -> None:
+        if rank == 0:
+            sys.stderr.write(f"[bench] {time.strftime('%H:%M:%S')} {msg}\n")
+            sys.stderr.flush()
+
     # ---------------------------------------------------------------- device-resident phase
+    note("device-resident phase: loading images")
     loader = open_loader()
     loader.add_filenames(owners)
     fb = loader.copy_files_to_device()
@@ -346,12 +352,15 @@ def b200_arm(args) -> dict:
                 "s_per_step": round(mean, 4), "steps": steps,
                 "page_cache": "dropped before every step" if cold else "warm"}
 
+    note(f"device-resident phase done: {resident_ms:.3f} ms per step")
     if not args.no_e2e and not args.kernel_only:
+        note("end-to-end phase, cold")
         mA = cpp.get_cpp_metrics()
         result["e2e"] = e2e_phase(True, args.steps, 1)
         mB = cpp.get_cpp_metrics()
         result["e2e"]["io"] = {"direct_requests": mB.direct_io_requests - mA.direct_io_requests,
                                "buffered_requests": mB.buffered_io_requests - mA.buffered_io_requests}
+        note("end-to-end phase, warm")
         if rank == 0:
             read_into_page_cache(paths)
         barrier()
@@ -360,16 +369,19 @@ def b200_arm(args) -> dict:
         mD = cpp.get_cpp_metrics()
         result["e2e_warm"]["io"] = {"direct_requests": mD.direct_io_requests - mC.direct_io_requests,
                                     "buffered_requests": mD.buffered_io_requests - mC.buffered_io_requests}
+        note("storage read roofline")
         result["storage_read"] = storage_roofline(paths, owners[rank], rank, barrier, max_over_ranks)
         if result["storage_read"]["cold_direct_gbs"]:
             result["e2e"]["frac_of_storage_read"] = round(
                 result["e2e"]["value"] / result["storage_read"]["cold_direct_gbs"], 3)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank == 0 and not args.no_cpu_baseline and not args.kernel_only:
+        note("cpu baseline (upstream on the host cores)")
         result["cpu_baseline"] = cpu_baseline(spec, paths)
         if world == 1:
             result["reference_cuda_nogds"] = reference_cuda_subprocess(args)
-    if world > 1:
-        dist.destroy_process_group()
     return result if rank == 0 else {}
 
 
@@ -418,8 +430,12 @@ def _reference_rank(rank: int, world: int, paths, plan_items, phases, port: int,
     torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
     pg = None
     if world > 1:
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        # an explicit tcp:// rendezvous of our own: drop what a launcher (torchrun) left in the
+        # environment, or every rank would wait as a client of the launcher's store
+        for key in [k for k in os.environ if k.startswith("TORCHELASTIC_")]:
+            os.environ.pop(key)
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank,
+                                world_size=world)
         pg = dist.group.WORLD
 
     def barrier():
@@ -462,7 +478,7 @@ def _reference_rank(rank: int, world: int, paths, plan_items, phases, port: int,
         dist.destroy_process_group()
 
 
-def run_reference(spec, paths, tp: int, phases) -> dict:
+def run_reference(spec, paths, tp: int, phases, timeout_s: float = 900.0) -> dict:
     import tempfile
 
     import torch.multiprocessing as mp
@@ -476,7 +492,14 @@ def run_reference(spec, paths, tp: int, phases) -> dict:
         if tp == 1:
             _reference_rank(0, 1, paths, plan_items, phases, port, out_path)
         else:
-            mp.spawn(_reference_rank, args=(tp, paths, plan_items, phases, port, out_path), nprocs=tp, join=True)
+            ctx = mp.start_processes(_reference_rank, args=(tp, paths, plan_items, phases, port, out_path),
+                                     nprocs=tp, join=False, start_method="spawn")
+            deadline = time.time() + timeout_s
+            while not ctx.join(timeout=5):
+                if time.time() > deadline:
+                    for p in ctx.processes:
+                        p.kill()
+                    raise TimeoutError(f"upstream CPU run exceeded {timeout_s} s")
         return json.load(open(out_path))
 
 
@@ -484,7 +507,7 @@ def cpu_baseline(spec, paths) -> dict:
     """Upstream on the host cores, one cold and one warm pass over the same checkpoint."""
     tp = spec.tp
     try:
-        t = run_reference(spec, paths, tp, [("cold", True, 1, 0), ("warm", False, 1, 0)])
+        t = run_reference(spec, paths, tp, [("cold", True, 1, 0), ("warm", False, 1, 0)], timeout_s=240.0)
     except Exception as e:  # noqa: BLE001
         return {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference",
                 "sample": f"failed: {type(e).__name__}: {e}"}

@@ -353,6 +353,8 @@ def b200_arm(args) -> dict:
                 "page_cache": "dropped before every step" if cold else "warm"}
 
     note(f"device-resident phase done: {resident_ms:.3f} ms per step")
+    if rank == 0:
+        result["other_kernels"] = other_kernels(device, peak)
     if not args.no_e2e and not args.kernel_only:
         note("end-to-end phase, cold")
         mA = cpp.get_cpp_metrics()
@@ -383,6 +385,47 @@ def b200_arm(args) -> dict:
         if world == 1:
             result["reference_cuda_nogds"] = reference_cuda_subprocess(args)
     return result if rank == 0 else {}
+
+
+def other_kernels(device: str, peak: float) -> dict:
+    """The path's other two kernels, timed alone with CUDA events on 1 GiB inputs (larger than
+    L2): fst_realign with the source 9 bytes off a 16-byte boundary (an odd header), and
+    fst_convert F32 -> BF16.  Algorithmic bytes: 2 x payload, and 4 + 2 bytes per element."""
+    import torch
+
+    from fastsafetensors_b200 import _native as nat
+
+    n = 1 << 30
+    stream = torch.cuda.current_stream()
+    out = {}
+
+    def timed(launch, alg_bytes):
+        for _ in range(3):
+            launch()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        a.record(stream)
+        for _ in range(reps):
+            launch()
+        b.record(stream)
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        gbs = alg_bytes / (ms * 1e-3) / GB
+        return {"avg_launch_ms": round(ms, 4), "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
+                "frac": round(gbs / peak, 4), "algorithmic_bytes_per_launch": int(alg_bytes)}
+
+    src = torch.empty(n + 64, dtype=torch.uint8, device=device)
+    dst = torch.empty(n + 64, dtype=torch.uint8, device=device)
+    out["fst_realign_kernel"] = timed(
+        lambda: nat.realign(dst.data_ptr(), src.data_ptr() + 9, n, stream.cuda_stream), 2.0 * n)
+    f32 = src[: n].view(torch.float32)
+    bf16 = dst[: n // 2].view(torch.bfloat16)
+    ops = [(f32.data_ptr(), bf16.data_ptr(), f32.numel(), nat.DT_CODES["F32"], nat.DT_CODES["BF16"])]
+    out["fst_convert_kernel"] = timed(lambda: nat.convert(ops, stream.cuda_stream), 1.5 * n)
+    del src, dst
+    torch.cuda.empty_cache()
+    return out
 
 
 def storage_roofline(paths, my_paths, rank, barrier, max_over_ranks) -> dict:

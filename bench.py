@@ -50,6 +50,11 @@ def parse_args():
     ap.add_argument("--dir", default=os.environ.get("FST_BENCH_DIR", "/tmp/fst_bench"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--warm-only", action="store_true", help="skip the cold end-to-end phase and the storage roofline")
+    ap.add_argument("--threads", type=int, default=int(os.environ.get("FST_BENCH_THREADS", 16)),
+                    help="reader threads (max_threads of the loader)")
+    ap.add_argument("--transport", default=os.environ.get("FST_B200_TRANSPORT", "nccl"), choices=("nccl", "peer"),
+                    help="N > 1: all_to_all over NCCL, or gather-kernel stores into peer arenas")
     ap.add_argument("--layers", type=int, default=0,
                     help="keep only the first L transformer layers (small case for profiler captures)")
     ap.add_argument("--kernel-only", action="store_true",
@@ -167,7 +172,7 @@ def b200_arm(args) -> dict:
     import fastsafetensors_b200 as fst
     from fastsafetensors_b200 import _native as nat
     from fastsafetensors_b200 import cpp, synth
-    from fastsafetensors_b200.batch import ShardExchange
+    from fastsafetensors_b200.batch import PeerShardExchange, ShardExchange
 
     rank, local_rank, world = dist_env()
     if not torch.cuda.is_available():
@@ -202,9 +207,11 @@ def b200_arm(args) -> dict:
 
     def open_loader():
         return fst.SafeTensorsFileLoader(pg if pg is not None else fst.SingleGroup(), torch.device(device),
-                                         nogds=True)
+                                         nogds=True, max_threads=args.threads)
 
     def make_exchange(fb) -> ShardExchange:
+        if world > 1 and args.transport == "peer":
+            return PeerShardExchange(fb, plan, tp, rank)
         return ShardExchange(fb, plan, tp, rank if world > 1 else 0, local=(world == 1))
 
     def note(msg: str) -> None:
@@ -243,17 +250,7 @@ def b200_arm(args) -> dict:
     barrier()
     start.record(stream)
     for _ in range(args.steps):
-        # ex.run() with an event pair around every gather launch
-        for arr, n, base, length in ex.launches:
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream)
-            nat.check(nat.lib.fst_gather(arr, n, 0, 0, base, length, stream.cuda_stream), "fst_gather")
-            b.record(stream)
-            kernel_events.append((a, b))
-        if world > 1:
-            lay = ex.layout
-            dist.all_to_all_single(ex.recv[:sum(lay.recv_sizes(rank))], ex.send, lay.recv_sizes(rank),
-                                   lay.send_sizes(rank), group=pg)
+        ex.run(timing=kernel_events)     # an event pair around every gather launch
     stop.record(stream)
     torch.cuda.synchronize()
     barrier()
@@ -267,8 +264,11 @@ def b200_arm(args) -> dict:
     alg_bytes_per_launch = 2.0 * payload_per_step * args.steps / max(1, n_launch)
     achieved = alg_bytes_per_launch / (kernel_ms * 1e-3) / GB if kernel_ms > 0 else 0.0
     clocks = sampler.stop() if sampler else None
+    egress = sum(ex.layout.region_bytes[rank][d] for d in range(tp) if d != rank) if world > 1 else 0
     # a light checksum of the result so the step has a device->host read
     check = int(ex.recv[:: max(1, ex.recv.numel() // 4096)].to(torch.int64).sum().item())
+    if isinstance(ex, PeerShardExchange):
+        ex.finish()
     del ex
     fb.close()
     loader.close()
@@ -295,7 +295,8 @@ def b200_arm(args) -> dict:
             "workload": f"{spec.name} ({args.scale}): {len(spec.tensors)} tensors, {len(paths)} files, "
                         f"{data_bytes} data bytes, tensor-parallel {tp}-way"
                         + (" packed by one rank for all destinations" if world == 1 else
-                           " files owned round-robin, NCCL all-to-all"),
+                           " files owned round-robin, " + ("NCCL all-to-all" if args.transport == "nccl"
+                                                            else "gather kernel stores into peer arenas (NVLink)")),
             "value_phase": "file images resident in HBM -> gather kernel (+ exchange)",
             "l2": f"inputs ({payload_per_step} B per rank and step) larger than L2 ({L2_BYTES} B), no flush",
             "tp": tp,
@@ -311,6 +312,13 @@ def b200_arm(args) -> dict:
         "clocks": clocks,
         "result_checksum": check,
     }
+    if world > 1:
+        # every byte a rank sends crosses NVLink once; with the step time this is the per-GPU
+        # egress rate the exchange sustains (measured peer-copy reference: 770 GB/s per direction)
+        result["nvlink"] = {"transport": args.transport, "egress_bytes_per_rank_and_step": int(egress),
+                            "egress_gbs_per_gpu": round(egress / (resident_ms * 1e-3) / GB, 1),
+                            "reference_peer_copy_gbs": 770.0,
+                            "note": "step time includes the gather kernel and the exchange"}
 
     # ---------------------------------------------------------------- end to end (public API)
     def e2e_step():
@@ -319,38 +327,49 @@ def b200_arm(args) -> dict:
         t0 = time.perf_counter()
         ld = open_loader()
         ld.add_filenames(owners)
+        t1 = time.perf_counter()
         buf = ld.copy_files_to_device()
+        t2 = time.perf_counter()
         if world == 1:
             got = buf.shard_locally(plan, tp)
             probe = next(iter(got[-1].values())).get_raw()
         else:
-            got = buf.exchange(plan)
+            got = buf.exchange(plan, transport=args.transport)
             probe = next(iter(got.values())).get_raw()
         head = probe.reshape(-1)[:1024].cpu()      # device -> host read of the result
         torch.cuda.synchronize()
         barrier()
-        dt = time.perf_counter() - t0
+        t3 = time.perf_counter()
         del got, probe
         buf.close()
         ld.close()
-        return max_over_ranks(dt), int(head.numel() * head.element_size())
+        return max_over_ranks(t3 - t0), int(head.numel() * head.element_size()), (t1 - t0, t2 - t1, t3 - t2)
 
     def e2e_phase(cold: bool, steps: int, warmup: int):
-        times, d2h = [], 0
+        times, d2h, parts = [], 0, []
+        r0 = cpp.get_cpp_metrics().read_ns
         for i in range(warmup + steps):
             if cold:
                 if rank == 0:
                     synth.drop_page_cache(paths)
                 barrier()
-            dt, d2h = e2e_step()
+            if i == warmup:
+                r0 = cpp.get_cpp_metrics().read_ns
+            dt, d2h, part = e2e_step()
             if i >= warmup:
                 times.append(dt)
+                parts.append(part)
             torch.cuda.empty_cache()
         mean = sum(times) / len(times)
+        read_s = (cpp.get_cpp_metrics().read_ns - r0) / 1e9 / len(times)
         return {"value": round(data_bytes / mean / GB, 3), "unit": "GB/s",
                 "h2d_bytes_per_step": int(data_bytes), "d2h_bytes_per_step": d2h,
                 "s_per_step": round(mean, 4), "steps": steps,
-                "page_cache": "dropped before every step" if cold else "warm"}
+                "page_cache": "dropped before every step" if cold else "warm",
+                "rank0_phases_s": {"open_and_headers": round(sum(p[0] for p in parts) / len(parts), 4),
+                                   "copy_files_to_device": round(sum(p[1] for p in parts) / len(parts), 4),
+                                   "shard_and_sync": round(sum(p[2] for p in parts) / len(parts), 4),
+                                   "pread_thread_seconds": round(read_s, 3)}}
 
     note(f"device-resident phase done: {resident_ms:.3f} ms per step")
     if rank == 0:
@@ -358,10 +377,11 @@ def b200_arm(args) -> dict:
     if not args.no_e2e and not args.kernel_only:
         note("end-to-end phase, cold")
         mA = cpp.get_cpp_metrics()
-        result["e2e"] = e2e_phase(True, args.steps, 1)
-        mB = cpp.get_cpp_metrics()
-        result["e2e"]["io"] = {"direct_requests": mB.direct_io_requests - mA.direct_io_requests,
-                               "buffered_requests": mB.buffered_io_requests - mA.buffered_io_requests}
+        if not args.warm_only:
+            result["e2e"] = e2e_phase(True, args.steps, 1)
+            mB = cpp.get_cpp_metrics()
+            result["e2e"]["io"] = {"direct_requests": mB.direct_io_requests - mA.direct_io_requests,
+                                   "buffered_requests": mB.buffered_io_requests - mA.buffered_io_requests}
         note("end-to-end phase, warm")
         if rank == 0:
             read_into_page_cache(paths)
@@ -371,9 +391,10 @@ def b200_arm(args) -> dict:
         mD = cpp.get_cpp_metrics()
         result["e2e_warm"]["io"] = {"direct_requests": mD.direct_io_requests - mC.direct_io_requests,
                                     "buffered_requests": mD.buffered_io_requests - mC.buffered_io_requests}
-        note("storage read roofline")
-        result["storage_read"] = storage_roofline(paths, owners[rank], rank, barrier, max_over_ranks)
-        if result["storage_read"]["cold_direct_gbs"]:
+        if not args.warm_only:
+            note("storage read roofline")
+            result["storage_read"] = storage_roofline(paths, owners[rank], rank, barrier, max_over_ranks)
+        if not args.warm_only and result["storage_read"]["cold_direct_gbs"]:
             result["e2e"]["frac_of_storage_read"] = round(
                 result["e2e"]["value"] / result["storage_read"]["cold_direct_gbs"], 3)
     if world > 1:

@@ -186,17 +186,30 @@ class ShardExchange:
         # (ctypes op array, count, destination base, destination length) per launch
         self.launches = [(nat.make_ops(g), len(g), buf.data_ptr(), buf.numel()) for g, buf in groups if g]
 
-    def run(self) -> None:
-        """Enqueue the gather launch(es) on torch's current stream, then the exchange."""
+    def _launch_gathers(self, timing: Optional[list]) -> None:
+        """Enqueue this rank's gather launches on torch's current stream.  With ``timing`` a
+        list, a pair of CUDA events brackets every launch and is appended to it."""
         from . import _native as nat
 
         if self.device.is_cpu:
             for arr, n, _, _ in self.launches:
                 nat.check(nat.lib.fst_gather_host(arr, n, 8), "fst_gather_host")
-        else:
-            stream = self.fb.framework.current_stream(self.device)
-            for arr, n, base, length in self.launches:
-                nat.check(nat.lib.fst_gather(arr, n, 0, 0, base, length, stream), "fst_gather")
+            return
+        stream = self.fb.framework.current_stream(self.device)
+        for arr, n, base, length in self.launches:
+            if timing is not None:
+                import torch
+
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+            nat.check(nat.lib.fst_gather(arr, n, 0, 0, base, length, stream), "fst_gather")
+            if timing is not None:
+                b.record()
+                timing.append((a, b))
+
+    def run(self, timing: Optional[list] = None) -> None:
+        """Enqueue the gather launch(es) on torch's current stream, then the exchange."""
+        self._launch_gathers(timing)
         if not self.local:
             import torch.distributed as dist
 
@@ -333,14 +346,10 @@ class PeerShardExchange(ShardExchange):
         self.launches = [(nat.make_ops(ops), len(ops), 0, 0)] if ops else []
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device.as_str())
 
-    def run(self) -> None:
+    def run(self, timing: Optional[list] = None) -> None:
         import torch.distributed as dist
 
-        from . import _native as nat
-
-        stream = self.fb.framework.current_stream(self.device)
-        for arr, n, base, length in self.launches:
-            nat.check(nat.lib.fst_gather(arr, n, 0, 0, base, length, stream), "fst_gather")
+        self._launch_gathers(timing)
         dist.all_reduce(self._flag, group=self.fb.pg.real_pg)   # stream-ordered barrier
 
     def finish(self) -> None:

@@ -5,7 +5,7 @@
 // for such a kernel on B200: 16-byte global loads and stores that a warp issues as whole
 // 512-byte rows (fully coalesced sectors on both sides), eight independent 16-byte loads in
 // flight per lane before the first store, streaming cache hints (the data is touched once),
-// and one step of work per CTA (see grid_limit_for for the measurement behind that).
+// and many short CTAs rather than a persistent grid (see grid_limit_for for the measurement).
 //
 // Work decomposition (gather).  An op is a strided 2-D byte copy (fst_copy2d_t).  Each row of
 // an op is cut into "subs" of at most SUB_BYTES; a sub is copied by one warp.  Sub boundaries
@@ -303,17 +303,23 @@ std::mutex g_ws_mutex;
 Workspace g_ws[MAX_DEVICES];
 int g_grid_limit[MAX_DEVICES];  // 0 = not computed yet
 
-// Grid size.  Measured on B200 (4 GiB flat copy, same inner loop): a persistent grid of
-// SMs x resident CTAs striding over the work reaches ~6.1 TB/s, the same kernel launched with one
-// step of work per CTA ~6.9 TB/s (cudaMemcpy device-to-device: ~6.6 TB/s).  The hardware block
-// scheduler hands out short CTAs in address order and keeps every SM equally loaded; a long
-// grid-stride loop lets CTAs drift apart and the DRAM pages they touch with them.  So the grid
-// is "as many CTAs as there are steps", bounded only by the launch limit; the stride loop in the
-// kernels remains for the (theoretical) case beyond it.  FST_B200_GRID_LIMIT overrides the
-// bound for experiments.
+// Grid size.  Measured on B200 on the 16 GB benchmark launch (2,328 ops, 7.8 M subs, 1965 MHz):
+//   persistent grid of 148 x 4 CTAs striding over the work      5.51 ms
+//   148 x 4 x 16 CTAs                                           5.09 ms
+//   148 x 4 x 64 CTAs                                           4.94 ms
+//   148 x 1024 CTAs (each CTA takes about three steps)          4.87 ms
+//   one step per CTA (490 k CTAs)                               5.04 ms
+// The hardware block scheduler hands out short CTAs in address order and keeps every SM equally
+// loaded; a long grid-stride loop lets CTAs drift apart, and the DRAM pages they touch with
+// them.  Beyond ~1000 CTAs per SM the per-CTA start-up (op lookup) begins to show.  So the grid
+// is min(steps, SMs x 1024).  FST_B200_GRID_LIMIT overrides the bound for experiments.
+constexpr int CTAS_PER_SM_BOUND = 1024;
 int grid_limit_for(int dev) {
     if (g_grid_limit[dev] == 0) {
-        int limit = 0x7fffffff;
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+        int limit = sms * CTAS_PER_SM_BOUND;
         if (const char *env = std::getenv("FST_B200_GRID_LIMIT"))
             if (std::atoi(env) > 0) limit = std::atoi(env);
         g_grid_limit[dev] = limit;

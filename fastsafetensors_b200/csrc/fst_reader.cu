@@ -127,6 +127,7 @@ class Reader {
   private:
     int start();  // streams, events, threads (first submit)
     int ensure_ring();
+    int ensure_stage_ring();
     void worker(int index);
     void run_task(const Task &t, Slot &slot, int worker_index);
     ssize_t do_pread(int fd, void *buf, size_t len, off_t off);
@@ -139,6 +140,7 @@ class Reader {
     uint64_t ring_bytes_ = 0;
     bool ring_pinned_ = false;
     uint64_t stage_bytes_ = 0;
+    unsigned char *stage_ring_ = nullptr;
     std::vector<Slot> slots_;
     std::vector<cudaStream_t> streams_;
     std::vector<std::thread> threads_;
@@ -191,6 +193,24 @@ int Reader::start() {
     return FST_OK;
 }
 
+// Allocates the device twin of the slot ring in ONE cudaMalloc, the first time a window needs the
+// realign kernel (cudaMalloc synchronises the device: one call, not one per slot).
+int Reader::ensure_stage_ring() {
+    std::lock_guard<std::mutex> lock(ring_mu_);
+    if (stage_ring_ != nullptr) return FST_OK;
+    const uint64_t bytes = (uint64_t)slots_.size() * cfg_.slot_bytes;
+    const cudaError_t e = cudaMalloc((void **)&stage_ring_, bytes);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        stage_ring_ = nullptr;
+        return FST_ENOMEM;
+    }
+    stage_bytes_ = bytes;
+    g_counters.staging_device_bytes.fetch_add(bytes);
+    for (size_t i = 0; i < slots_.size(); ++i) slots_[i].stage = stage_ring_ + i * cfg_.slot_bytes;
+    return FST_OK;
+}
+
 // Allocates the slot ring on first need.  A host destination read through the page cache is
 // filled in place and never needs it.  Callers hold no lock; ring_mu_ serialises the workers.
 int Reader::ensure_ring() {
@@ -239,11 +259,11 @@ void Reader::shutdown() {
         cudaStreamDestroy(s);
     }
     streams_.clear();
-    for (auto &s : slots_) {
+    for (auto &s : slots_)
         if (s.done) cudaEventDestroy(s.done);
-        if (s.stage) cudaFree(s.stage);
-    }
     slots_.clear();
+    if (stage_ring_) cudaFree(stage_ring_);
+    stage_ring_ = nullptr;
     if (stage_bytes_) g_counters.staging_device_bytes.fetch_sub(stage_bytes_);
     stage_bytes_ = 0;
     if (ring_) {
@@ -439,18 +459,11 @@ void Reader::run_task(const Task &t, Slot &slot, int worker_index) {
         e = cudaMemcpyAsync((void *)(uintptr_t)t.dst, src, t.valid_len, cudaMemcpyHostToDevice, st);
     } else {
         if (slot.stage == nullptr) {
-            e = cudaMalloc((void **)&slot.stage, cfg_.slot_bytes);
-            if (e != cudaSuccess) {
-                std::snprintf(msg, sizeof(msg), "cudaMalloc(staging slot, %llu) failed: %s",
-                              (unsigned long long)cfg_.slot_bytes, cudaGetErrorString(e));
-                finish(t, FST_ENOMEM, msg, 0);
+            const int rc = ensure_stage_ring();
+            if (rc != FST_OK) {
+                finish(t, rc, "device staging ring allocation failed", 0);
                 return;
             }
-            {
-                std::lock_guard<std::mutex> lock(mu_);
-                stage_bytes_ += cfg_.slot_bytes;
-            }
-            g_counters.staging_device_bytes.fetch_add(cfg_.slot_bytes);
         }
         // 16-byte envelope of the valid bytes inside the slot (slot start is page aligned)
         const uint64_t first = t.valid_off - t.win_off;

@@ -9,14 +9,16 @@ has not been built.
 
 __version__ = "0.1.0"
 
+from .auto_loader import AutoLoader
 from .common import SafeTensorsMetadata, SingleGroup, TensorFrame, get_device_numa_node
+from .config import LoaderConfig, load_config
 from .file_buffer import FilesBufferOnDevice
 from .loader import BaseSafeTensorsFileLoader, SafeTensorsFileLoader, fastsafe_open
 from .parallel_loader import ParallelLoader, PipelineParallel
 from .st_types import Device, DeviceType, DType
 
 __all__ = [
-    "BaseSafeTensorsFileLoader", "Device", "DeviceType", "DType", "FilesBufferOnDevice",
+    "AutoLoader", "LoaderConfig", "load_config", "BaseSafeTensorsFileLoader", "Device", "DeviceType", "DType", "FilesBufferOnDevice",
     "ParallelLoader", "PipelineParallel", "SafeTensorsFileLoader", "SafeTensorsMetadata", "SingleGroup", "TensorFrame",
     "fastsafe_open", "get_device_numa_node",
 ]

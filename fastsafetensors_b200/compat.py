@@ -17,7 +17,7 @@ _TARGET = "fastsafetensors_b200"
 _SUBMODULES = (
     "", ".cpp", ".common", ".st_types", ".loader", ".file_buffer", ".tensor_factory",
     ".frameworks", ".frameworks._torch", ".copier", ".copier.base", ".copier.registry",
-    ".copier.nogds", ".copier.gds", ".parallel_loader",
+    ".copier.nogds", ".copier.gds", ".parallel_loader", ".config", ".auto_loader",
 )
 
 

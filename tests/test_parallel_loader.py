@@ -105,3 +105,28 @@ def test_two_ranks_every_rank_gets_every_tensor(queue_size, case_files, tmp_path
     for rank in range(2):
         got = json.load(open(tmp_path / f"rank{rank}.json"))
         assert got == want, rank
+
+
+def test_auto_loader_reads_its_configuration(case_files, tmp_path, monkeypatch, leak_check):
+    """AutoLoader: settings come from $FASTSAFETENSORS_CONFIG (upstream docs/configuration.md)."""
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps({
+        "loader": "base", "base": {"copier_type": "nogds", "max_threads": 2, "debug_log": True},
+        "parallel": {"use_pipeline": True, "queue_size": 1, "use_tqdm_on_load": False, "bogus": 1},
+        "debug": {"set_numa": False}, "unknown": 3,
+    }))
+    monkeypatch.setenv("FASTSAFETENSORS_CONFIG", str(cfg))
+    paths = sorted(case_files(CASE))[:4]
+    it = fst.AutoLoader(None, paths, device="cpu")
+    assert it.config.queue_size == 1 and it.config.use_pipeline and it.config.set_numa is False
+    assert it.config.get_extension_config("base") == {"copier_type": "nogds", "max_threads": 2}
+    got = {k: (list(t.shape), digest_tensor(t)) for k, t in it.iterate_weights()}
+    it.close()
+    assert got == _expected(paths)
+    monkeypatch.setenv("FASTSAFETENSORS_CONFIG", str(tmp_path / "nope.json"))
+    with pytest.raises(FileNotFoundError):
+        fst.load_config()
+    monkeypatch.delenv("FASTSAFETENSORS_CONFIG")
+    assert fst.load_config().create_parallel_kwargs() == {"queue_size": -1}
+    with pytest.raises(ValueError):
+        fst.LoaderConfig(max_concurrent_producers=2)

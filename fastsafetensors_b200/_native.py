@@ -30,7 +30,7 @@ ABI_VERSION = 1
 OK, EINVAL, ERANGE, ENOCUDA, ECUDA, EIO, ETIMEOUT, ENOMEM, ELIMIT, EGDS = (
     0, -1, -2, -3, -4, -5, -6, -7, -8, -9,
 )
-IO_AUTO, IO_DIRECT, IO_BUFFERED = 0, 1, 2
+IO_AUTO, IO_DIRECT, IO_BUFFERED, IO_CUFILE = 0, 1, 2, 3
 GATHER_INLINE_OPS = 48
 GATHER_STATIC_MAX_OPS = 4096
 ARENA_HANDLE_BYTES = 64
@@ -44,6 +44,7 @@ EXPORTS = (
     "fst_reader_inject_fault", "fst_gather", "fst_gather_static", "fst_gather_host",
     "fst_realign", "fst_release_workspaces", "fst_arena_create", "fst_arena_export",
     "fst_arena_open_peer", "fst_arena_close_peer", "fst_arena_destroy", "fst_convert",
+    "fst_cufile_available", "fst_gds_supported",
 )
 
 
@@ -145,6 +146,7 @@ def _load() -> ctypes.CDLL:
     lib.fst_gather_host.argtypes = [POINTER(Copy2D), c_uint64, c_int]
     lib.fst_realign.argtypes = [c_uint64, c_uint64, c_uint64, c_uint64]
     lib.fst_release_workspaces.restype = c_int
+    lib.fst_gds_supported.argtypes = [c_int]
     lib.fst_convert.argtypes = [POINTER(ConvertOp), c_uint64, c_uint64]
     lib.fst_arena_create.argtypes = [c_uint64, POINTER(c_uint64)]
     lib.fst_arena_export.argtypes = [c_uint64, c_void_p, c_uint64]

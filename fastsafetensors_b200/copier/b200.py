@@ -24,7 +24,8 @@ from .base import CopierInterface
 from .registry import CopierConstructFunc, register_copier_constructor
 
 DEFAULT_SLOT_KB = 4096
-_IO_MODES = {"auto": nat.IO_AUTO, "direct": nat.IO_DIRECT, "buffered": nat.IO_BUFFERED}
+_IO_MODES = {"auto": nat.IO_AUTO, "direct": nat.IO_DIRECT, "buffered": nat.IO_BUFFERED,
+             "cufile": nat.IO_CUFILE}
 
 
 class B200FileCopier(CopierInterface):
@@ -59,6 +60,8 @@ class B200FileCopier(CopierInterface):
             try:
                 self.reader.wait(request)
             except nat.NativeError as e:
+                if e.code == nat.EGDS:
+                    raise          # a RuntimeError naming "gds": callers retry without it
                 raise Exception(f"wait_io: read of {self.metadata.src} failed: {e}") from e
         if dtype != DType.AUTO and self.device.type != DeviceType.CPU:
             tensors = self.metadata.get_tensors(gbuf, self.device, self.metadata.header_length)
@@ -124,8 +127,10 @@ def new_b200_file_copier(device: Device, bbuf_size_kb: int = 16 * 1024, max_thre
     ``bbuf_size_kb`` keeps upstream's meaning of a total ring size but only as a lower bound:
     each worker gets two slots of at least ``slot_kb`` KiB (default 4 MiB, or the
     ``FST_B200_SLOT_KB`` environment variable), large enough for direct I/O and DMA to run at
-    full rate.  ``io_mode`` is ``"auto"`` (default, or ``FST_B200_IO_MODE``), ``"direct"`` or
-    ``"buffered"``.
+    full rate.  ``io_mode`` is ``"auto"`` (default, or ``FST_B200_IO_MODE``), ``"direct"``,
+    ``"buffered"`` or ``"cufile"`` (``cuFileRead`` into a registered device staging ring; a
+    ``RuntimeError`` whose text contains "gds" is raised where cuFile cannot be used, which is
+    what callers such as vLLM catch to retry with ``nogds=True``).
     """
     on_gpu = device.type != DeviceType.CPU
     if on_gpu and nat.cuda_device_count() == 0:

@@ -257,7 +257,7 @@ def is_hip_found() -> bool:
 
 
 def is_cufile_found() -> bool:
-    return False
+    return bool(nat.lib.fst_cufile_available())
 
 
 def cufile_version() -> int:
@@ -265,7 +265,7 @@ def cufile_version() -> int:
 
 
 def is_gds_supported(deviceId: int) -> int:
-    return 0
+    return int(nat.lib.fst_gds_supported(deviceId))
 
 
 def init_gds() -> int:

@@ -14,6 +14,8 @@
 // realign kernel shifts it to d on the same stream; the copy engine only ever sees 16-byte
 // aligned addresses, and the shift costs 2 x payload of HBM traffic instead of a slower DMA.
 #include <cuda_runtime.h>
+#include <cufile.h>
+#include <dlfcn.h>
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -40,6 +42,68 @@ namespace fst {
 namespace {
 
 constexpr uint64_t IO_ALIGN = 4096;
+
+// cuFile entry points, resolved from libcufile.so at run time (the library is optional).
+struct CuFileApi {
+    CUfileError_t (*DriverOpen)() = nullptr;
+    CUfileError_t (*DriverClose)() = nullptr;
+    CUfileError_t (*HandleRegister)(CUfileHandle_t *, CUfileDescr_t *) = nullptr;
+    void (*HandleDeregister)(CUfileHandle_t) = nullptr;
+    CUfileError_t (*BufRegister)(const void *, size_t, int) = nullptr;
+    CUfileError_t (*BufDeregister)(const void *) = nullptr;
+    ssize_t (*Read)(CUfileHandle_t, void *, size_t, off_t, off_t) = nullptr;
+    bool loaded = false;
+    bool tried = false;
+    int driver_users = 0;
+};
+CuFileApi g_cufile;
+std::mutex g_cufile_mutex;
+
+bool load_cufile_locked() {
+    if (g_cufile.tried) return g_cufile.loaded;
+    g_cufile.tried = true;
+    void *h = nullptr;
+    for (const char *name : {"libcufile.so.0", "libcufile.so"}) {
+        h = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+        if (h) break;
+    }
+    if (!h) return false;
+    auto sym = [&](const char *n) { return dlsym(h, n); };
+    g_cufile.DriverOpen = (decltype(g_cufile.DriverOpen))sym("cuFileDriverOpen");
+    g_cufile.DriverClose = (decltype(g_cufile.DriverClose))sym("cuFileDriverClose");
+    g_cufile.HandleRegister = (decltype(g_cufile.HandleRegister))sym("cuFileHandleRegister");
+    g_cufile.HandleDeregister = (decltype(g_cufile.HandleDeregister))sym("cuFileHandleDeregister");
+    g_cufile.BufRegister = (decltype(g_cufile.BufRegister))sym("cuFileBufRegister");
+    g_cufile.BufDeregister = (decltype(g_cufile.BufDeregister))sym("cuFileBufDeregister");
+    g_cufile.Read = (decltype(g_cufile.Read))sym("cuFileRead");
+    g_cufile.loaded = g_cufile.DriverOpen && g_cufile.HandleRegister && g_cufile.HandleDeregister &&
+                      g_cufile.BufRegister && g_cufile.BufDeregister && g_cufile.Read;
+    return g_cufile.loaded;
+}
+
+// Opens the cuFile driver for one more user.  Returns FST_OK or FST_EGDS (error text set).
+int cufile_acquire() {
+    std::lock_guard<std::mutex> lock(g_cufile_mutex);
+    if (!load_cufile_locked()) {
+        set_error("gds: libcufile.so could not be loaded");
+        return FST_EGDS;
+    }
+    if (g_cufile.driver_users == 0) {
+        const CUfileError_t e = g_cufile.DriverOpen();
+        if (e.err != CU_FILE_SUCCESS) {
+            set_error("gds: cuFileDriverOpen failed with cuFile error %d", (int)e.err);
+            return FST_EGDS;
+        }
+    }
+    ++g_cufile.driver_users;
+    return FST_OK;
+}
+
+void cufile_release() {
+    std::lock_guard<std::mutex> lock(g_cufile_mutex);
+    if (g_cufile.driver_users > 0 && --g_cufile.driver_users == 0 && g_cufile.DriverClose)
+        g_cufile.DriverClose();
+}
 
 inline uint64_t align_down(uint64_t v, uint64_t a) { return v - v % a; }
 inline uint64_t align_up(uint64_t v, uint64_t a) { return align_down(v + a - 1, a); }
@@ -85,6 +149,8 @@ struct Request {
     int64_t id = 0;
     int fd = -1;
     bool direct = false;
+    bool cufile = false;
+    CUfileHandle_t cf_handle = nullptr;
     uint64_t remaining = 0;   // windows not yet handed to the copy engine / destination
     uint64_t bytes_done = 0;
     int status = FST_OK;
@@ -130,6 +196,7 @@ class Reader {
     int ensure_stage_ring();
     void worker(int index);
     void run_task(const Task &t, Slot &slot, int worker_index);
+    void run_cufile_task(const Task &t, Slot &slot, int worker_index);
     ssize_t do_pread(int fd, void *buf, size_t len, off_t off);
     void finish(const Task &t, int status, const std::string &err, uint64_t bytes);
 
@@ -139,6 +206,8 @@ class Reader {
     unsigned char *ring_ = nullptr;
     uint64_t ring_bytes_ = 0;
     bool ring_pinned_ = false;
+    bool cufile_open_ = false;       // this reader holds a reference on the cuFile driver
+    bool stage_registered_ = false;  // the staging ring is registered with cuFile
     uint64_t stage_bytes_ = 0;
     unsigned char *stage_ring_ = nullptr;
     std::vector<Slot> slots_;
@@ -185,8 +254,24 @@ int Reader::start() {
         }
         // a device destination always goes through the ring: allocate it now, on the caller's
         // thread, so that a failure is reported by submit
-        const int rc = ensure_ring();
-        if (rc != FST_OK) return rc;
+        if (cfg_.io_mode == FST_IO_CUFILE) {
+            // cuFile lands file windows in the device staging ring directly; no host ring
+            int rc = cufile_acquire();
+            if (rc != FST_OK) return rc;
+            cufile_open_ = true;
+            rc = ensure_stage_ring();
+            if (rc != FST_OK) {
+                set_error("gds: device staging ring allocation failed");
+                return rc;
+            }
+            const CUfileError_t e2 = g_cufile.BufRegister(stage_ring_, stage_bytes_, 0);
+            stage_registered_ = e2.err == CU_FILE_SUCCESS;  // unregistered buffers still work
+            FST_DEBUG("reader: cuFile staging ring of %llu bytes, registered=%d",
+                      (unsigned long long)stage_bytes_, (int)stage_registered_);
+        } else {
+            const int rc = ensure_ring();
+            if (rc != FST_OK) return rc;
+        }
     }
     started_ = true;
     for (int i = 0; i < cfg_.threads; ++i) threads_.emplace_back(&Reader::worker, this, i);
@@ -262,8 +347,12 @@ void Reader::shutdown() {
     for (auto &s : slots_)
         if (s.done) cudaEventDestroy(s.done);
     slots_.clear();
+    if (stage_registered_) g_cufile.BufDeregister(stage_ring_);
+    stage_registered_ = false;
     if (stage_ring_) cudaFree(stage_ring_);
     stage_ring_ = nullptr;
+    if (cufile_open_) cufile_release();
+    cufile_open_ = false;
     if (stage_bytes_) g_counters.staging_device_bytes.fetch_sub(stage_bytes_);
     stage_bytes_ = 0;
     if (ring_) {
@@ -272,11 +361,14 @@ void Reader::shutdown() {
         g_counters.bounce_buffer_bytes.fetch_sub(ring_bytes_);
         ring_ = nullptr;
     }
-    for (auto &kv : requests_)
+    for (auto &kv : requests_) {
+        if (kv.second->cf_handle) g_cufile.HandleDeregister(kv.second->cf_handle);
+        kv.second->cf_handle = nullptr;
         if (kv.second->fd >= 0) {
             close(kv.second->fd);
             kv.second->fd = -1;
         }
+    }
     requests_.clear();
 }
 
@@ -297,6 +389,11 @@ int Reader::submit(const char *path, uint64_t file_off, uint64_t nbytes, uint64_
     int flags = O_RDONLY | O_CLOEXEC;
     int fd = -1;
     bool direct = cfg_.io_mode != FST_IO_BUFFERED;
+    const bool cufile = cfg_.io_mode == FST_IO_CUFILE;
+    if (cufile && cfg_.device < 0) {
+        set_error("gds: cuFile reads need a device destination");
+        return FST_EGDS;
+    }
     if (cfg_.io_mode == FST_IO_AUTO) {
         fd = open(path, flags);
         if (fd >= 0) {
@@ -329,6 +426,19 @@ int Reader::submit(const char *path, uint64_t file_off, uint64_t nbytes, uint64_
     }
     req->fd = fd;
     req->direct = direct;
+    if (cufile) {
+        CUfileDescr_t descr;
+        std::memset(&descr, 0, sizeof(descr));
+        descr.handle.fd = fd;
+        descr.type = CU_FILE_HANDLE_TYPE_OPAQUE_FD;
+        const CUfileError_t e = g_cufile.HandleRegister(&req->cf_handle, &descr);
+        if (e.err != CU_FILE_SUCCESS) {
+            set_error("gds: cuFileHandleRegister(%s) failed with cuFile error %d", path, (int)e.err);
+            close(fd);
+            return FST_EGDS;
+        }
+        req->cufile = true;
+    }
     (direct ? g_counters.direct_io_requests : g_counters.buffered_io_requests).fetch_add(1);
 
     const uint64_t end = file_off + nbytes;
@@ -348,6 +458,8 @@ int Reader::submit(const char *path, uint64_t file_off, uint64_t nbytes, uint64_
     requests_[req->id] = req;
     *out_id = req->id;
     if (count == 0) {
+        if (req->cf_handle) g_cufile.HandleDeregister(req->cf_handle);
+        req->cf_handle = nullptr;
         close(req->fd);
         req->fd = -1;
     }
@@ -383,6 +495,8 @@ void Reader::finish(const Task &t, int status, const std::string &err, uint64_t 
     }
     r.bytes_done += bytes;
     if (--r.remaining == 0) {
+        if (r.cf_handle) g_cufile.HandleDeregister(r.cf_handle);
+        r.cf_handle = nullptr;
         if (r.fd >= 0) close(r.fd);
         r.fd = -1;
         done_cv_.notify_all();
@@ -395,6 +509,10 @@ void Reader::run_task(const Task &t, Slot &slot, int worker_index) {
     char msg[256];
     if (r.status != FST_OK) {  // the request already failed: drain without I/O
         finish(t, FST_OK, "", 0);
+        return;
+    }
+    if (r.cufile) {
+        run_cufile_task(t, slot, worker_index);
         return;
     }
     const uint64_t t0 = now_ns();
@@ -482,6 +600,55 @@ void Reader::run_task(const Task &t, Slot &slot, int worker_index) {
     }
     slot.pending = true;
     g_counters.bytes_h2d.fetch_add(t.valid_len, std::memory_order_relaxed);
+    finish(t, FST_OK, "", t.valid_len);
+}
+
+// cuFile variant of a window: cuFileRead lands the 4096-aligned file window in the slot's device
+// twin (DMA from storage where GPUDirect Storage is active, cuFile's own bounce otherwise), then
+// the realign kernel moves the wanted bytes to their place (a plain vector copy when source and
+// destination are congruent modulo 16).
+void Reader::run_cufile_task(const Task &t, Slot &slot, int worker_index) {
+    Request &r = *t.req;
+    char msg[256];
+    if (slot.pending) {
+        cudaEventSynchronize(slot.done);
+        slot.pending = false;
+    }
+    const uint64_t t0 = now_ns();
+    const uint64_t need = t.valid_off + t.valid_len - t.win_off;
+    const off_t ring_off = (off_t)(slot.stage - stage_ring_);
+    uint64_t got = 0;
+    while (got < need) {
+        const ssize_t c = g_cufile.Read(r.cf_handle, stage_ring_, t.win_len - got,
+                                        (off_t)(t.win_off + got), ring_off + (off_t)got);
+        if (c < 0) {
+            std::snprintf(msg, sizeof(msg), "gds: cuFileRead(offset=%llu) failed: %zd (errno %d)",
+                          (unsigned long long)(t.win_off + got), c, errno);
+            finish(t, FST_EGDS, msg, 0);
+            return;
+        }
+        if (c == 0) break;
+        got += (uint64_t)c;
+    }
+    g_counters.read_ns.fetch_add(now_ns() - t0, std::memory_order_relaxed);
+    g_counters.bytes_read.fetch_add(got, std::memory_order_relaxed);
+    if (got < need) {
+        std::snprintf(msg, sizeof(msg), "gds: short cuFileRead: wanted %llu bytes at offset %llu, got %llu",
+                      (unsigned long long)need, (unsigned long long)t.win_off, (unsigned long long)got);
+        finish(t, FST_EIO, msg, 0);
+        return;
+    }
+    cudaStream_t st = streams_[worker_index % streams_.size()];
+    cudaError_t e = (cudaError_t)launch_realign((void *)(uintptr_t)t.dst,
+                                                slot.stage + (t.valid_off - t.win_off), t.valid_len,
+                                                (void *)st);
+    if (e == cudaSuccess) e = cudaEventRecord(slot.done, st);
+    if (e != cudaSuccess) {
+        std::snprintf(msg, sizeof(msg), "gds: staging to destination copy failed: %s", cudaGetErrorString(e));
+        finish(t, FST_ECUDA, msg, 0);
+        return;
+    }
+    slot.pending = true;
     finish(t, FST_OK, "", t.valid_len);
 }
 
@@ -577,7 +744,7 @@ extern "C" int fst_reader_create(const fst_reader_config_t *cfg, uint64_t *reade
     }
     fst_reader_config_t c = *cfg;
     if (c.threads < 1 || c.threads > 1024 || c.slots_per_thread < 1 || c.slots_per_thread > 64 ||
-        c.slot_bytes == 0 || c.io_mode < FST_IO_AUTO || c.io_mode > FST_IO_BUFFERED) {
+        c.slot_bytes == 0 || c.io_mode < FST_IO_AUTO || c.io_mode > FST_IO_CUFILE) {
         set_error("fst_reader_create: bad configuration (threads=%d, slots_per_thread=%d, "
                   "slot_bytes=%llu, io_mode=%d)", c.threads, c.slots_per_thread,
                   (unsigned long long)c.slot_bytes, c.io_mode);
@@ -652,4 +819,16 @@ extern "C" int fst_reader_inject_fault(uint64_t reader, int64_t nth, int err, in
     }
     r->inject(nth, err, short_bytes);
     return FST_OK;
+}
+
+extern "C" int fst_cufile_available(void) {
+    std::lock_guard<std::mutex> lock(g_cufile_mutex);
+    return load_cufile_locked() ? 1 : 0;
+}
+
+extern "C" int fst_gds_supported(int device) {
+    (void)device;
+    // GPUDirect Storage proper needs the nvidia-fs kernel module; without it cuFile can only run
+    // in its compatibility mode (POSIX reads + copies inside the library)
+    return access("/proc/driver/nvidia-fs/stats", F_OK) == 0 ? 1 : 0;
 }

@@ -125,6 +125,8 @@ int fst_get_metrics(fst_metrics_t *out);
 #define FST_IO_AUTO 0     /* direct I/O unless most of the file is resident in the page cache */
 #define FST_IO_DIRECT 1   /* O_DIRECT; falls back to buffered if the filesystem refuses it   */
 #define FST_IO_BUFFERED 2 /* plain pread through the page cache                              */
+#define FST_IO_CUFILE 3   /* cuFileRead into the registered device staging ring (device dst only);
+                             FST_EGDS, with "gds" in the error text, when cuFile cannot be used  */
 
 typedef struct fst_reader_config {
     int32_t device;           /* CUDA device of destinations; -1: destinations are host memory */
@@ -160,6 +162,12 @@ int fst_reader_wait(uint64_t reader, int64_t request, int64_t timeout_ms, uint64
 /* Join the workers, free ring, staging ring and streams.  Replaces ~nogds_file_reader
  * (ext.cpp:778-806). */
 int fst_reader_destroy(uint64_t reader);
+
+/* 1 if libcufile.so can be loaded.  Replaces is_cufile_found() (cpp.pyi). */
+int fst_cufile_available(void);
+/* 1 if GPUDirect Storage proper can work for this device (the nvidia-fs module is loaded), 0 if
+ * cuFile could only run in its compatibility mode.  Replaces is_gds_supported() (ext.cpp:444-478). */
+int fst_gds_supported(int device);
 
 /* Host-side fault injection for tests: the nth pread from now on (1-based, counted over all
  * workers of this reader) fails with `err` (an errno value), or, if short_bytes >= 0,

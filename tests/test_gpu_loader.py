@@ -257,3 +257,51 @@ def test_loader_narrowing_on_cuda_matches_torch(tmp_path, leak_check):
     with pytest.raises(Exception, match="larger sizes"):
         loader.copy_files_to_device(dtype=DType.F64)
     loader.close()
+
+
+# ------------------------------------------------------------------ cuFile window source
+@pytest.mark.parametrize("offset", [0, 4096, 8 + 1, 123456 + 8])
+def test_reader_cufile_mode(blob_file, offset, leak_check):
+    """io_mode cufile: cuFileRead lands windows in the registered device staging ring, the
+    realign kernel places them.  Where cuFile cannot be used at all the reader must say so with
+    an error that names "gds" (callers fall back on that), and the test is skipped."""
+    path, data = blob_file
+    length = data.size - offset
+    if not cpp.is_cufile_found():
+        pytest.skip("libcufile.so is not installed")
+    reader = cpp.Reader(0, 4, 1 << 20, 2, io_mode=nat.IO_CUFILE, copy_streams=2)
+    try:
+        dst = torch.full((length + 512,), 0x5A, dtype=torch.uint8, device=DEV)
+        buf = cpp.gds_device_buffer(dst.data_ptr(), dst.numel(), True)
+        try:
+            rid = reader.submit(path, offset, length, buf, 256)
+        except nat.NativeError as e:
+            assert e.code == nat.EGDS and "gds" in str(e)
+            pytest.skip(f"cuFile is not usable on this machine: {e}")
+        assert reader.wait(rid, 120000) == length
+        got = dst.cpu().numpy()
+        assert np.array_equal(got[256:256 + length], data[offset:])
+        assert (got[:256] == 0x5A).all() and (got[256 + length:] == 0x5A).all()
+    finally:
+        reader.close()
+    assert cpp.get_cpp_metrics().staging_device_bytes == 0
+
+
+def test_loader_with_cufile_matches_upstream(golden, case_files, leak_check):
+    case = [c for c in cases.CASES if c["id"] == "llama2_13b_w1_gds"][0]   # odd headers
+    paths = case_files(case)
+    if not cpp.is_cufile_found():
+        pytest.skip("libcufile.so is not installed")
+    loader = fst.SafeTensorsFileLoader(fst.SingleGroup(), DEV, nogds=False, io_mode="cufile", max_threads=4,
+                                       slot_kb=256)
+    loader.add_filenames({0: paths})
+    try:
+        fb = loader.copy_files_to_device()
+    except RuntimeError as e:
+        assert "gds" in str(e)
+        loader.close()
+        pytest.skip(f"cuFile is not usable on this machine: {e}")
+    got = {name: record(fb.get_tensor(name)) for name, _ in cases.plan(case)}
+    assert got == golden["cases"][case["id"]][0]
+    fb.close()
+    loader.close()

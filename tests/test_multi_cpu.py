@@ -88,3 +88,80 @@ def test_gloo_ranks_match_upstream(case, batched, golden, case_files, tmp_path):
     for rank in range(world):
         got = json.load(open(tmp_path / f"rank{rank}.json"))
         assert got == golden["cases"][case["id"]][rank], f"rank {rank}"
+
+
+# ------------------------------------------------------------------ packed / 8-bit float dtypes
+PACKED = [
+    # name, dtype, shape (safetensors element counts), dim
+    ("f4_rows", "F4", (8, 16), 0), ("f4_cols", "F4", (4, 32), 1), ("e8m0", "F8_E8M0", (6, 10), 1),
+    ("e5m2", "F8_E5M2", (6, 8), 0), ("e4m3", "F8_E4M3", (4, 12), 1),
+]
+
+
+def _write_packed(path):
+    import numpy as np
+
+    from fastsafetensors_b200 import synth
+    from oracle import st_oracle
+
+    rng = np.random.default_rng(77)
+    entries, blobs, off = {}, [], 0
+    for name, dtype, shape, _ in PACKED:
+        n = int(np.prod(shape)) * st_oracle.BITS[dtype] // 8
+        entries[name] = {"dtype": dtype, "shape": list(shape), "data_offsets": [off, off + n]}
+        blobs.append(rng.integers(0, 120, n, dtype=np.uint8).tobytes())
+        off += n
+    with open(path, "wb") as f:
+        f.write(synth.header_bytes(entries, odd=False))
+        f.write(b"".join(blobs))
+
+
+def _packed_rank(rank, world, path, port, out_dir):
+    sys.path.insert(0, ROOT)
+    import fastsafetensors_b200 as fst
+    from tests.helpers import digest_tensor
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    loader = fst.SafeTensorsFileLoader(dist.group.WORLD, "cpu", nogds=True, max_threads=2)
+    loader.add_filenames({1: [path]})          # owned by rank 1
+    fb = loader.copy_files_to_device()
+    out = {}
+    for name, _, _, dim in PACKED:
+        t = fb.get_sharded(name, dim)
+        out[name] = [list(t.shape), str(t.dtype), digest_tensor(t)]
+    fb.close()
+    loader.close()
+    loader = fst.SafeTensorsFileLoader(dist.group.WORLD, "cpu", nogds=True, max_threads=2)
+    loader.add_filenames({1: [path]})
+    fb = loader.copy_files_to_device()
+    got = fb.exchange(OrderedDict((name, ("shard", dim)) for name, _, _, dim in PACKED))
+    for name, t in got.items():
+        assert out[name][2] == digest_tensor(t), name      # batched path agrees
+    fb.close()
+    loader.close()
+    with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
+        json.dump(out, f)
+    dist.destroy_process_group()
+
+
+def test_packed_and_8bit_float_dtypes_shard_as_bytes(tmp_path):
+    """F4 (two values per byte), F8_E8M0, F8_E5M2, F8_E4M3: shards must be the oracle's byte
+    slices; F4 shapes shrink on the last dimension in torch's packed dtype (upstream
+    _torch.py:331-350).  Upstream itself cannot scatter E5M2/E4M3 over gloo; bytes can."""
+    from oracle import st_oracle
+    from tests.helpers import digest_bytes
+
+    path = str(tmp_path / "packed.safetensors")
+    _write_packed(path)
+    world = 2
+    mp.spawn(_packed_rank, args=(world, path, 29990, str(tmp_path)), nprocs=world, join=True)
+    fo = st_oracle.FileOracle(path)
+    for rank in range(world):
+        got = json.load(open(tmp_path / f"rank{rank}.json"))
+        for name, dtype, shape, dim in PACKED:
+            raw, new_shape = fo.get_sharded(name, dim, rank, world)
+            if dtype == "F4":
+                new_shape = new_shape[:-1] + [new_shape[-1] // 2]
+            assert got[name][0] == new_shape, name
+            assert got[name][2] == digest_bytes(raw), (name, rank)

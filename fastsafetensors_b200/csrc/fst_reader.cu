@@ -89,7 +89,9 @@ int cufile_acquire() {
         return FST_EGDS;
     }
     if (g_cufile.driver_users == 0) {
+        FST_DEBUG("cufile: calling cuFileDriverOpen");
         const CUfileError_t e = g_cufile.DriverOpen();
+        FST_DEBUG("cufile: cuFileDriverOpen returned %d", (int)e.err);
         if (e.err != CU_FILE_SUCCESS) {
             set_error("gds: cuFileDriverOpen failed with cuFile error %d", (int)e.err);
             return FST_EGDS;
@@ -264,6 +266,7 @@ int Reader::start() {
                 set_error("gds: device staging ring allocation failed");
                 return rc;
             }
+            FST_DEBUG("cufile: registering the staging ring");
             const CUfileError_t e2 = g_cufile.BufRegister(stage_ring_, stage_bytes_, 0);
             stage_registered_ = e2.err == CU_FILE_SUCCESS;  // unregistered buffers still work
             FST_DEBUG("reader: cuFile staging ring of %llu bytes, registered=%d",
@@ -431,7 +434,9 @@ int Reader::submit(const char *path, uint64_t file_off, uint64_t nbytes, uint64_
         std::memset(&descr, 0, sizeof(descr));
         descr.handle.fd = fd;
         descr.type = CU_FILE_HANDLE_TYPE_OPAQUE_FD;
+        FST_DEBUG("cufile: registering the file handle");
         const CUfileError_t e = g_cufile.HandleRegister(&req->cf_handle, &descr);
+        FST_DEBUG("cufile: cuFileHandleRegister returned %d", (int)e.err);
         if (e.err != CU_FILE_SUCCESS) {
             set_error("gds: cuFileHandleRegister(%s) failed with cuFile error %d", path, (int)e.err);
             close(fd);
@@ -619,8 +624,11 @@ void Reader::run_cufile_task(const Task &t, Slot &slot, int worker_index) {
     const off_t ring_off = (off_t)(slot.stage - stage_ring_);
     uint64_t got = 0;
     while (got < need) {
+        FST_DEBUG("cufile: cuFileRead(offset=%llu, size=%llu)", (unsigned long long)(t.win_off + got),
+                  (unsigned long long)(t.win_len - got));
         const ssize_t c = g_cufile.Read(r.cf_handle, stage_ring_, t.win_len - got,
                                         (off_t)(t.win_off + got), ring_off + (off_t)got);
+        FST_DEBUG("cufile: cuFileRead returned %zd", c);
         if (c < 0) {
             std::snprintf(msg, sizeof(msg), "gds: cuFileRead(offset=%llu) failed: %zd (errno %d)",
                           (unsigned long long)(t.win_off + got), c, errno);

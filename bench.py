@@ -55,6 +55,8 @@ def parse_args():
                     help="reader threads (max_threads of the loader)")
     ap.add_argument("--transport", default=os.environ.get("FST_B200_TRANSPORT", "nccl"), choices=("nccl", "peer"),
                     help="N > 1: all_to_all over NCCL, or gather-kernel stores into peer arenas")
+    ap.add_argument("--ref-budget", type=float, default=150.0,
+                    help="--impl reference: seconds the cold phase may take before it is cut to fewer files")
     ap.add_argument("--layers", type=int, default=0,
                     help="keep only the first L transformer layers (small case for profiler captures)")
     ap.add_argument("--kernel-only", action="store_true",
@@ -304,7 +306,13 @@ def b200_arm(args) -> dict:
         "gpu_launches": int(launches_timed),
         "roofline": {
             "bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-            "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
+            "frac": round(achieved / peak, 4),
+            # dram read+write bytes of one launch: the ncu capture of a small case of this kernel
+            # gave 0.993 x its algorithmic bytes (no re-reads); traffic grows in proportion
+            "traffic": int(0.993 * alg_bytes_per_launch) if world == 1 else None,
+            "traffic_source": "ncu small case x units processed (profiles/fst_gather_kernel_llama3-8b.md)"
+                              if world == 1 else None,
+            "peak_source": peak_src,
             "kernel": "fst_gather_kernel", "launches": n_launch,
             "avg_launch_ms": round(kernel_ms, 4),
             "algorithmic_bytes_per_launch": int(alg_bytes_per_launch),
@@ -513,21 +521,26 @@ def _reference_rank(rank: int, world: int, paths, plan_items, phases, port: int,
         if world > 1:
             dist.barrier()
 
-    owners = synth.owners(paths, world)
     results = {}
-    for label, cold, steps, warmup in phases:
-        times = []
+    for label, cold, steps, warmup, budget_s in phases:
+        samples = []            # (seconds, bytes) per timed step
+        n_files = len(paths)
         for i in range(warmup + steps):
+            use = sorted(paths)[:n_files]
+            owners = synth.owners(use, world)
             if cold:
                 if rank == 0:
-                    synth.drop_page_cache(paths)
+                    synth.drop_page_cache(use)
             barrier()
             t0 = time.perf_counter()
             loader = ref.SafeTensorsFileLoader(pg if pg is not None else ref.SingleGroup(), "cpu", nogds=True)
             loader.add_filenames(owners)
             fb = loader.copy_files_to_device()
+            present = set(fb.key_to_rank_lidx)
             keep = []
             for name, action in plan_items:
+                if name not in present:
+                    continue
                 if action[0] == "shard":
                     keep.append(fb.get_sharded(name, action[1]))
                 elif action[0] == "replicate":
@@ -536,12 +549,26 @@ def _reference_rank(rank: int, world: int, paths, plan_items, phases, port: int,
                     keep.append(fb.push_tensor(name, action[1]))
             barrier()
             dt = time.perf_counter() - t0
+            nbytes = sum(m.size_bytes - m.header_length for m, _ in loader.meta.values())
             del keep
             fb.close()
             loader.close()
             if i >= warmup:
-                times.append(dt)
-        results[label] = times
+                samples.append((dt, nbytes))
+            if i == 0:
+                # bounded sample: if the remaining steps would not fit the phase's budget, go on
+                # with the first files only (rank 0 decides, everyone follows)
+                left = warmup + steps - 1
+                decision = [n_files]
+                if rank == 0 and left > 0 and dt * left > budget_s:
+                    decision = [max(1, int(len(paths) * budget_s / (dt * left)))]
+                if world > 1:
+                    dist.broadcast_object_list(decision, src=0)
+                if decision[0] != n_files:
+                    n_files = decision[0]
+                    samples = []   # a step over the full set is not comparable any more
+        results[label] = {"seconds": [s_[0] for s_ in samples], "bytes": [s_[1] for s_ in samples],
+                          "files": n_files}
     if rank == 0:
         with open(out_path, "w") as f:
             json.dump(results, f)
@@ -577,11 +604,11 @@ def run_reference(spec, paths, tp: int, phases, timeout_s: float = 900.0) -> dic
 def cpu_baseline(spec, paths, tp: int) -> dict:
     """Upstream on the host cores, one cold and one warm pass over the same checkpoint."""
     try:
-        t = run_reference(spec, paths, tp, [("cold", True, 1, 0), ("warm", False, 1, 0)], timeout_s=240.0)
+        t = run_reference(spec, paths, tp, [("cold", True, 1, 0, 1e9), ("warm", False, 1, 0, 1e9)], timeout_s=240.0)
     except Exception as e:  # noqa: BLE001
         return {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference",
                 "sample": f"failed: {type(e).__name__}: {e}"}
-    cold, warm = t["cold"][0], t["warm"][0]
+    cold, warm = t["cold"]["seconds"][0], t["warm"]["seconds"][0]
     return {"value": round(spec.data_bytes / cold / GB, 3), "unit": "GB/s", "cores": os.cpu_count(),
             "kind": "reference",
             "sample": f"upstream fastsafetensors 0.3.2, device cpu, nogds, {tp} gloo ranks, whole "
@@ -612,14 +639,17 @@ def reference_arm(args) -> dict:
     spec = load_spec(args)
     tp = spec.tp if world == 1 else world
     paths = prepare_files(spec, args.dir, 0, lambda: None)
-    phases = [("cold", True, args.steps, 1), ("warm", False, min(args.steps, 3), 1)]
+    phases = [("cold", True, args.steps, 1, args.ref_budget), ("warm", False, min(args.steps, 3), 1, 40.0)]
     t = run_reference(spec, paths, tp, phases)
-    cold = sum(t["cold"]) / len(t["cold"])
-    warm = sum(t["warm"]) / len(t["warm"])
-    v = round(spec.data_bytes / cold / GB, 3)
+
+    def rate(ph):
+        return sum(ph["bytes"]) / sum(ph["seconds"]) / GB
+
+    cold = sum(t["cold"]["seconds"]) / len(t["cold"]["seconds"])
+    v = round(rate(t["cold"]), 3)
     sample = (f"upstream fastsafetensors 0.3.2 (oracle/_ref), device cpu, nogds, {tp} gloo ranks on "
-              f"{os.cpu_count()} cores, whole {spec.name} checkpoint per step, page cache dropped "
-              f"before every step")
+              f"{os.cpu_count()} cores, {t['cold']['files']} of {len(paths)} files of the {spec.name} "
+              f"checkpoint per step, page cache dropped before every step")
     return {
         "impl": "reference",
         "metric": "safetensors->HBM tensor-parallel load throughput",
@@ -632,7 +662,7 @@ def reference_arm(args) -> dict:
                          "sample": sample},
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                 "page_cache": "dropped before every step"},
-        "e2e_warm": {"value": round(spec.data_bytes / warm / GB, 3), "unit": "GB/s"},
+        "e2e_warm": {"value": round(rate(t["warm"]), 3), "unit": "GB/s", "files": t["warm"]["files"]},
         "gpu_launches": 0,
     }
 

@@ -46,35 +46,20 @@ class Device:
         return self.type == DeviceType.CPU
 
 
-class DType(enum.Enum):
-    BOOL = "BOOL"
-    I8 = "I8"
-    I16 = "I16"
-    I32 = "I32"
-    I64 = "I64"
-    U8 = "U8"
-    U16 = "U16"
-    U32 = "U32"
-    U64 = "U64"
-    F16 = "F16"
-    F32 = "F32"
-    F64 = "F64"
-    BF16 = "BF16"
-    F8_E5M2 = "F8_E5M2"
-    F8_E4M3 = "F8_E4M3"
-    F8_E8M0 = "F8_E8M0"
-    F4 = "F4"
-    AUTO = "AUTO"
-
+class _DTypeBase(enum.Enum):
     @property
     def bits(self) -> int:
         """Bits per logical element in a safetensors file (F4 packs two values per byte)."""
-        return _BITS[self]
+        return _BITS[self.value]
 
 
+# dtype strings of the safetensors format (member name == value), plus AUTO = "as stored"
 _BITS = {
-    DType.BOOL: 8, DType.I8: 8, DType.U8: 8, DType.F8_E5M2: 8, DType.F8_E4M3: 8,
-    DType.F8_E8M0: 8, DType.I16: 16, DType.U16: 16, DType.F16: 16, DType.BF16: 16,
-    DType.I32: 32, DType.U32: 32, DType.F32: 32, DType.I64: 64, DType.U64: 64,
-    DType.F64: 64, DType.F4: 4,
+    "BOOL": 8, "I8": 8, "U8": 8, "F8_E5M2": 8, "F8_E4M3": 8, "F8_E8M0": 8,
+    "I16": 16, "U16": 16, "F16": 16, "BF16": 16,
+    "I32": 32, "U32": 32, "F32": 32,
+    "I64": 64, "U64": 64, "F64": 64,
+    "F4": 4,
 }
+DType = _DTypeBase("DType", {name: name for name in list(_BITS) + ["AUTO"]})
+DType.__doc__ = "Element type of a tensor in a safetensors file; ``AUTO`` means: keep what the file has."

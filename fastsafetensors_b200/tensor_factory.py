@@ -26,8 +26,13 @@ from .frameworks import ProcessGroupBase, TensorBase
 from .frameworks._torch import TorchTensor
 from .st_types import Device, DeviceType, DType
 
+import os
+
 logger = init_logger(__name__)
 HOST_GATHER_THREADS = 8
+# fraction of a file that may be broadcast tensor by tensor before the whole image is broadcast
+# instead (0 disables the switch); see LazyTensorFactory.shuffle
+REPLICATE_FILE_AFTER = float(os.environ.get("FST_B200_REPLICATE_FILE_AFTER", "0.25"))
 
 
 class LazyTensorFactory:
@@ -48,6 +53,7 @@ class LazyTensorFactory:
         self.disable_cache = disable_cache
         self.replicated = False             # every rank holds the image (see replicate)
         self.converted = False              # tensors were narrowed in place at load time
+        self.broadcast_bytes = 0            # bytes handed out one tensor at a time with dim -1
 
     # ---------------------------------------------------------------- file -> image
     def submit_io(self, use_buf_register: bool, max_copy_block_size: int) -> None:
@@ -153,6 +159,15 @@ class LazyTensorFactory:
             return self.shuffled[tensor_name].clone().detach()
         frame = self.metadata.tensors[tensor_name]
         owner = self.rank == pg.rank()
+        if dim == -1 and not self.replicated and not self.converted and REPLICATE_FILE_AFTER > 0:
+            # A caller that asks for whole tensors one after the other (vLLM's loader asks for
+            # every key) is better served by ONE broadcast of the file image than by a broadcast
+            # per tensor.  Once a quarter of the file has gone out tensor by tensor, the rest
+            # goes in one piece.  Every rank sees the same requests, so all switch together.
+            self.broadcast_bytes += frame.data_offsets[1] - frame.data_offsets[0]
+            image_bytes = self.metadata.size_bytes - self.metadata.header_length
+            if self.broadcast_bytes >= image_bytes * REPLICATE_FILE_AFTER:
+                self.replicate(pg)
         if dim == -1 and self.replicated:
             return self._owned("shuffle", tensor_name)   # view of this rank's copy of the image
         if dim == -1:

@@ -8,7 +8,7 @@ import torch
 import torch.multiprocessing as mp
 
 from tests.golden import cases
-from tests.test_multi_cpu import _rank_main
+from tests.test_multi_cpu import _all_keys_rank, _rank_main
 
 pytestmark = pytest.mark.gpu
 MULTI = [c for c in cases.CASES if c["world"] > 1]
@@ -29,3 +29,23 @@ def test_nccl_ranks_match_upstream(case, batched, golden, case_files, tmp_path):
     for rank in range(world):
         got = json.load(open(tmp_path / f"rank{rank}.json"))
         assert got == golden["cases"][case["id"]][rank], f"rank {rank}"
+
+
+def test_every_key_access_over_nccl(case_files, tmp_path):
+    """The vLLM access pattern (get_tensor of every key) on two GPUs: results byte-identical to
+    the files, served by one image broadcast per file after the first few tensors."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from oracle import st_oracle
+    from tests.helpers import digest_bytes
+
+    case = [c for c in cases.CASES if c["id"] == "llama3_8b_w2_cols"][0]
+    paths = sorted(case_files(case))[:2]
+    mp.spawn(_all_keys_rank, args=(2, paths, 29996, str(tmp_path), "nccl"), nprocs=2, join=True)
+    want = {}
+    for p in paths:
+        fo = st_oracle.FileOracle(p)
+        for n in fo.tensors:
+            want[n] = digest_bytes(fo.raw(n))
+    for rank in range(2):
+        assert json.load(open(tmp_path / f"rank{rank}.json")) == want

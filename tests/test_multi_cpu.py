@@ -165,3 +165,60 @@ def test_packed_and_8bit_float_dtypes_shard_as_bytes(tmp_path):
                 new_shape = new_shape[:-1] + [new_shape[-1] // 2]
             assert got[name][0] == new_shape, name
             assert got[name][2] == digest_bytes(raw), (name, rank)
+
+
+# ------------------------------------------------------------------ "every key" access pattern
+def _all_keys_rank(rank, world, paths, port, out_dir, backend="gloo"):
+    sys.path.insert(0, ROOT)
+    import fastsafetensors_b200 as fst
+    from fastsafetensors_b200 import cpp
+    from tests.helpers import digest_tensor
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    if backend == "nccl":
+        torch.cuda.set_device(rank)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+        device = f"cuda:{rank}"
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        device = "cpu"
+    calls = {"n": 0}
+    real = dist.broadcast
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+
+    dist.broadcast = counting
+    loader = fst.SafeTensorsFileLoader(dist.group.WORLD, device, nogds=True, max_threads=2, slot_kb=64)
+    loader.add_filenames({i: [p] for i, p in enumerate(paths)})
+    fb = loader.copy_files_to_device()
+    out = {}
+    for k in list(fb.key_to_rank_lidx.keys()):         # what vLLM's iterator does
+        out[k] = digest_tensor(fb.get_tensor(k))
+    n_keys = len(out)
+    fb.close()
+    loader.close()
+    assert loader.framework.get_mem_used() == 0
+    # far fewer collectives than tensors: per file a few tensor broadcasts, then one for the image
+    assert calls["n"] < n_keys // 2, (calls["n"], n_keys)
+    with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
+        json.dump(out, f)
+    dist.destroy_process_group()
+
+
+def test_asking_for_every_key_switches_to_one_broadcast_per_file(case_files, tmp_path):
+    from oracle import st_oracle
+    from tests.helpers import digest_bytes
+
+    case = [c for c in cases.CASES if c["id"] == "llama3_8b_w2_cols"][0]
+    paths = sorted(case_files(case))[:2]
+    mp.spawn(_all_keys_rank, args=(2, paths, 29995, str(tmp_path)), nprocs=2, join=True)
+    want = {}
+    for p in paths:
+        fo = st_oracle.FileOracle(p)
+        for n in fo.tensors:
+            want[n] = digest_bytes(fo.raw(n))
+    for rank in range(2):
+        assert json.load(open(tmp_path / f"rank{rank}.json")) == want

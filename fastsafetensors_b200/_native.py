@@ -20,7 +20,7 @@ from ctypes import (
     c_uint64,
     c_void_p,
 )
-from typing import Iterable, List, Sequence, Tuple
+from typing import Sequence, Tuple
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libfst_b200.so")
 

@@ -17,7 +17,7 @@ import os
 from typing import Any, Dict, Optional
 
 from .. import _native as nat
-from ..common import SafeTensorsMetadata, get_device_numa_node
+from ..common import SafeTensorsMetadata
 from ..cpp import Reader, gds_device_buffer, gds_file_reader
 from ..st_types import Device, DeviceType, DType
 from .base import CopierInterface

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import os
 from collections import OrderedDict
-from typing import Any, Dict, List, Optional, Set, Tuple
+from typing import Any, Dict, List, Optional, Tuple
 
 from .common import init_logger
 from .frameworks import ProcessGroupBase, TensorBase

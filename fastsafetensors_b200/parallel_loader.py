@@ -30,7 +30,6 @@ except ImportError:  # pragma: no cover
         return iterable
 
 from . import cpp as fstcpp
-from .common import SingleGroup
 from .loader import BaseSafeTensorsFileLoader, SafeTensorsFileLoader
 
 _BAR_FORMAT = "{desc}: {percentage:3.0f}% Completed | {n_fmt}/{total_fmt} [{elapsed}<{remaining}, {rate_fmt}]\n"

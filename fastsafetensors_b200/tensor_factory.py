@@ -16,7 +16,7 @@ Same role and method names as upstream ``fastsafetensors/tensor_factory.py``
 
 from __future__ import annotations
 
-from typing import Any, Dict, List, Optional
+from typing import Dict, List, Optional
 
 from . import _native as nat
 from . import shard_plan
@@ -24,7 +24,7 @@ from .common import SafeTensorsMetadata, init_logger
 from .copier.base import CopierInterface, DummyDeviceBuffer
 from .frameworks import ProcessGroupBase, TensorBase
 from .frameworks._torch import TorchTensor
-from .st_types import Device, DeviceType, DType
+from .st_types import Device, DType
 
 import os
 

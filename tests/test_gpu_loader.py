@@ -11,9 +11,8 @@ import torch
 
 import fastsafetensors_b200 as fst
 from fastsafetensors_b200 import _native as nat
-from fastsafetensors_b200 import cpp, shard_plan, synth
+from fastsafetensors_b200 import cpp, shard_plan
 from fastsafetensors_b200.batch import BatchLayout
-from fastsafetensors_b200.frameworks import get_framework_op
 from oracle import st_oracle
 from tests.golden import cases
 from tests.helpers import digest_bytes, record, tensor_bytes

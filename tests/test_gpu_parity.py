@@ -4,7 +4,6 @@ Everything goes through the C ABI (fst_gather, fst_realign, fst_reader_*) or thr
 API built on it.  Integer/byte work: every comparison is bit-exact."""
 
 import os
-from collections import OrderedDict
 
 import numpy as np
 import pytest
@@ -12,12 +11,8 @@ import torch
 
 import fastsafetensors_b200 as fst
 from fastsafetensors_b200 import _native as nat
-from fastsafetensors_b200 import cpp, shard_plan, synth
-from fastsafetensors_b200.batch import BatchLayout
-from fastsafetensors_b200.frameworks import get_framework_op
+from fastsafetensors_b200 import cpp, shard_plan
 from oracle import st_oracle
-from tests.golden import cases
-from tests.helpers import digest_bytes, record, tensor_bytes
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"

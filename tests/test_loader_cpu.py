@@ -262,3 +262,21 @@ def test_shard_locally_produces_every_ranks_tensors(case, golden, case_files, le
         assert {k: record(v) for k, v in tensors.items()} == want
     fb.close()
     loader.close()
+
+
+def test_fix_alignment_pads_the_header_only(case_files, tmp_path, leak_check):
+    from fastsafetensors_b200.fix_alignment import aligned_copy
+
+    case = [c for c in cases.CASES if c["id"] == "llama2_13b_w4"][0]     # odd header lengths
+    src = sorted(case_files(case))[0]
+    dst = str(tmp_path / "aligned.safetensors")
+    assert aligned_copy(src, dst) is True
+    a, b = st_oracle.FileOracle(src), st_oracle.FileOracle(dst)
+    assert a.header_length % 16 != 0 and b.header_length % 16 == 0
+    assert a.metadata == b.metadata and list(a.tensors) == list(b.tensors)
+    for n in a.tensors:
+        assert a.tensors[n] == b.tensors[n] and np.array_equal(a.raw(n), b.raw(n))
+    assert aligned_copy(dst, str(tmp_path / "again.safetensors")) is False
+    with fst.fastsafe_open(dst, device="cpu", nogds=True) as f:
+        k = f.keys()[0]
+        assert digest_bytes(tensor_bytes(f.get_tensor(k))) == digest_bytes(a.raw(k))

@@ -190,23 +190,30 @@ class ShardExchange:
         ops = lay.fill_ops(me, mine, src_addr, region) if mine else []
         self.payload_bytes = sum(o[2] * o[3] for o in ops)
         lo, hi = self.recv.data_ptr(), self.recv.data_ptr() + self.recv.numel()
-        groups = [([o for o in ops if lo <= o[1] < hi], self.recv)]
-        if self.send is not None:
-            groups.append(([o for o in ops if not (lo <= o[1] < hi)], self.send))
-        # (ctypes op array, count, destination base, destination length) per launch
-        self.launches = [(nat.make_ops(g), len(g), buf.data_ptr(), buf.numel()) for g, buf in groups if g]
+        outgoing = [o for o in ops if not (lo <= o[1] < hi)]
+        own = [o for o in ops if lo <= o[1] < hi]
+        # (ctypes op array, count, destination base, destination length) per launch.  What has
+        # to travel is packed first, so that the exchange can start while this rank's own
+        # region is still being packed (see run).
+        self.launches = []
+        if self.send is not None and outgoing:
+            self.launches.append((nat.make_ops(outgoing), len(outgoing), self.send.data_ptr(), self.send.numel()))
+        self.n_outgoing_launches = len(self.launches)
+        if own:
+            self.launches.append((nat.make_ops(own), len(own), self.recv.data_ptr(), self.recv.numel()))
 
-    def _launch_gathers(self, timing: Optional[list]) -> None:
-        """Enqueue this rank's gather launches on torch's current stream.  With ``timing`` a
-        list, a pair of CUDA events brackets every launch and is appended to it."""
+    def _launch_gathers(self, timing: Optional[list], which: Optional[slice] = None) -> None:
+        """Enqueue gather launches (all, or ``self.launches[which]``) on torch's current stream.
+        With ``timing`` a list, a pair of CUDA events brackets every launch and is appended."""
         from . import _native as nat
 
+        todo = self.launches if which is None else self.launches[which]
         if self.device.is_cpu:
-            for arr, n, _, _ in self.launches:
+            for arr, n, _, _ in todo:
                 nat.check(nat.lib.fst_gather_host(arr, n, 8), "fst_gather_host")
             return
         stream = self.fb.framework.current_stream(self.device)
-        for arr, n, base, length in self.launches:
+        for arr, n, base, length in todo:
             if timing is not None:
                 import torch
 
@@ -218,15 +225,22 @@ class ShardExchange:
                 timing.append((a, b))
 
     def run(self, timing: Optional[list] = None) -> None:
-        """Enqueue the gather launch(es) on torch's current stream, then the exchange."""
-        self._launch_gathers(timing)
-        if not self.local:
-            import torch.distributed as dist
+        """Pack and exchange.  The outgoing regions are packed first and the ``all_to_all`` is
+        started asynchronously; this rank's own region is packed while the exchange runs (the two
+        write disjoint parts of the receive buffer); then the stream waits for the exchange."""
+        if self.local:
+            self._launch_gathers(timing)
+            return
+        import torch.distributed as dist
 
-            lay, me = self.layout, self.me
-            incoming = sum(lay.recv_sizes(me))
-            dist.all_to_all_single(self.recv[:incoming], self.send, lay.recv_sizes(me),
-                                   lay.send_sizes(me), group=self.fb.pg.real_pg)
+        k = self.n_outgoing_launches
+        self._launch_gathers(timing, slice(0, k))
+        lay, me = self.layout, self.me
+        incoming = sum(lay.recv_sizes(me))
+        work = dist.all_to_all_single(self.recv[:incoming], self.send, lay.recv_sizes(me),
+                                      lay.send_sizes(me), group=self.fb.pg.real_pg, async_op=True)
+        self._launch_gathers(timing, slice(k, None))
+        work.wait()
 
     def _view(self, slot: Slot, off: int):
         from .frameworks._torch import TorchTensor, dtype_convert

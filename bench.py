@@ -59,6 +59,8 @@ def parse_args():
                     help="--impl reference: seconds the cold phase may take before it is cut to fewer files")
     ap.add_argument("--layers", type=int, default=0,
                     help="keep only the first L transformer layers (small case for profiler captures)")
+    ap.add_argument("--other-kernels-only", action="store_true",
+                    help="only the stand-alone timing of the realign and convert kernels (for profiler captures)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the device-resident phase (for profiler captures)")
     return ap.parse_args()
@@ -200,6 +202,10 @@ def b200_arm(args) -> dict:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    if args.other_kernels_only:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
+        return {"other_kernels": other_kernels(device, peak)} if rank == 0 else {}
     spec = load_spec(args)
     tp = spec.tp if world == 1 else world
     plan = plan_for(spec, tp)

@@ -254,8 +254,6 @@ int Reader::start() {
                 return FST_ECUDA;
             }
         }
-        // a device destination always goes through the ring: allocate it now, on the caller's
-        // thread, so that a failure is reported by submit
         if (cfg_.io_mode == FST_IO_CUFILE) {
             // cuFile lands file windows in the device staging ring directly; no host ring
             int rc = cufile_acquire();

@@ -140,8 +140,10 @@ typedef struct fst_reader_config {
     int32_t reserved[7];
 } fst_reader_config_t;
 
-/* Create a reader.  The ring is allocated lazily at the first submit (as upstream does,
- * ext.cpp:735-751) and counted in fst_metrics.bounce_buffer_bytes. */
+/* Create a reader.  Nothing is allocated yet: streams, events and threads come with the first
+ * submit, and every worker pins its own slots when it gets its first window (upstream pins its
+ * whole bounce buffer at the first submit, ext.cpp:735-751).  Pinned bytes are counted in
+ * fst_metrics.bounce_buffer_bytes. */
 int fst_reader_create(const fst_reader_config_t *cfg, uint64_t *reader);
 
 /* Queue the read of file bytes [file_offset, file_offset + nbytes) of `path` into

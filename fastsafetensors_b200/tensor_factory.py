@@ -16,6 +16,7 @@ Same role and method names as upstream ``fastsafetensors/tensor_factory.py``
 
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 from . import _native as nat
@@ -25,8 +26,6 @@ from .copier.base import CopierInterface, DummyDeviceBuffer
 from .frameworks import ProcessGroupBase, TensorBase
 from .frameworks._torch import TorchTensor
 from .st_types import Device, DType
-
-import os
 
 logger = init_logger(__name__)
 HOST_GATHER_THREADS = 8

@@ -9,8 +9,9 @@ here keeps those variables and that return triple.  The policy behind it is the 
 
 * threads: the logical CPUs of the GPU's node that this process may run on, divided among the
   ranks of the machine (one process per GPU all read at once), between 2 and 16.  Logical, not
-  physical as upstream counts: a worker either sleeps in ``pread`` or copies out of the page
-  cache, and on a 16-vCPU host 16 workers moved more bytes per second than 8;
+  physical as upstream counts: a worker mostly sleeps in an ``O_DIRECT`` ``pread``, and what a
+  cold read needs is requests in flight, not cores.  (From the page cache 8 and 16 workers moved
+  the same bytes per second on a 16-vCPU host, 32 fewer: the ring's pinning cost grows with it.)
 * pinned memory: two slots per thread of ``DEFAULT_SLOT_KB`` each (windows of that size keep a
   cold ``O_DIRECT`` stream at the device's rate and still pipeline within one file); pinning goes
   through the CUDA driver and is not charged to ``RLIMIT_MEMLOCK``, so that limit is not consulted;

@@ -1,6 +1,8 @@
 """Reader settings from the host topology (a fake sysfs tree) and from upstream's environment
 variables (examples/tgis_weight.py:19-55)."""
 
+import pytest
+
 from fastsafetensors_b200 import tune
 
 
@@ -104,5 +106,28 @@ def test_settings_drive_a_loader(tmp_path):
     loader.add_filenames({0: [path]})
     fb = loader.copy_files_to_device()
     assert np.array_equal(fb.get_tensor("t").numpy(), raw)
+    fb.close()
+    loader.close()
+
+
+@pytest.mark.gpu
+def test_suggested_settings_load_onto_the_gpu(tmp_path):
+    """The tuner asks the native library for the device's NUMA node; whatever it answers, the
+    suggested settings must load a file onto the device byte for byte."""
+    import numpy as np
+    import torch
+    from safetensors.torch import save_file
+
+    import fastsafetensors_b200 as fst
+
+    s = tune.suggest(0)
+    assert 2 <= s.max_threads <= 16 and s.bbuf_size_kb == s.max_threads * 2 * s.slot_kb
+    path = str(tmp_path / "g.safetensors")
+    raw = np.random.default_rng(5).integers(0, 256, (3 << 20) + 17, dtype=np.uint8)
+    save_file({"t": torch.from_numpy(raw.copy())}, path)
+    loader = fst.SafeTensorsFileLoader(fst.SingleGroup(), "cuda:0", **s.loader_kwargs())
+    loader.add_filenames({0: [path]})
+    fb = loader.copy_files_to_device()
+    assert np.array_equal(fb.get_tensor("t").cpu().numpy(), raw)
     fb.close()
     loader.close()

@@ -53,8 +53,10 @@ def parse_args():
     ap.add_argument("--warm-only", action="store_true", help="skip the cold end-to-end phase and the storage roofline")
     ap.add_argument("--threads", type=int, default=int(os.environ.get("FST_BENCH_THREADS", 16)),
                     help="reader threads (max_threads of the loader)")
-    ap.add_argument("--transport", default=os.environ.get("FST_B200_TRANSPORT", "nccl"), choices=("nccl", "peer"),
-                    help="N > 1: all_to_all over NCCL, or gather-kernel stores into peer arenas")
+    ap.add_argument("--transport", default=os.environ.get("FST_B200_TRANSPORT", "auto"),
+                    choices=("auto", "nccl", "peer"),
+                    help="N > 1: all_to_all over NCCL, gather-kernel stores into peer arenas, or the "
+                         "library's own choice (peer for two ranks, else NCCL)")
     ap.add_argument("--ref-budget", type=float, default=150.0,
                     help="--impl reference: seconds the cold phase may take before it is cut to fewer files")
     ap.add_argument("--layers", type=int, default=0,
@@ -176,7 +178,8 @@ def b200_arm(args) -> dict:
     import fastsafetensors_b200 as fst
     from fastsafetensors_b200 import _native as nat
     from fastsafetensors_b200 import cpp, synth
-    from fastsafetensors_b200.batch import PeerShardExchange, ShardExchange
+    from fastsafetensors_b200.batch import PeerArenaUnavailable, PeerShardExchange, ShardExchange
+    from fastsafetensors_b200.file_buffer import resolve_transport
 
     rank, local_rank, world = dist_env()
     if not torch.cuda.is_available():
@@ -217,9 +220,23 @@ def b200_arm(args) -> dict:
         return fst.SafeTensorsFileLoader(pg if pg is not None else fst.SingleGroup(), torch.device(device),
                                          nogds=True, max_threads=args.threads)
 
+    # "auto" is the library's rule: the fused peer exchange where it measured faster (two ranks),
+    # the NCCL all-to-all otherwise, and NCCL on all ranks together if peer mapping is refused
+    may_fall_back = False
+    if world > 1:
+        want = resolve_transport(args.transport, world, fst.Device.from_str(device))
+        may_fall_back = want == "auto"
+        args.transport = "nccl" if want == "nccl" else "peer"
+
     def make_exchange(fb) -> ShardExchange:
         if world > 1 and args.transport == "peer":
-            return PeerShardExchange(fb, plan, tp, rank)
+            try:
+                return PeerShardExchange(fb, plan, tp, rank)
+            except PeerArenaUnavailable as e:     # every rank gets it at the same call
+                if not may_fall_back:
+                    raise
+                note(f"peer arenas unavailable ({e}); NCCL all-to-all instead")
+                args.transport = "nccl"
         return ShardExchange(fb, plan, tp, rank if world > 1 else 0, local=(world == 1))
 
     def note(msg: str) -> None:

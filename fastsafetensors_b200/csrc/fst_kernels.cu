@@ -23,7 +23,8 @@
 // aligned), a body of 16-byte destination vectors, up to 15 tail bytes.  If the source is
 // congruent to the destination modulo 16 the body is a plain vector copy; if not, each
 // destination vector is assembled from the two aligned 16-byte source words that straddle it
-// with funnel shifts.  The aligned words read may extend up to 15 bytes before or after the
+// with funnel shifts (a lane loads the first and gets the second from the next lane by
+// shuffle).  The aligned words read may extend up to 15 bytes before or after the
 // source range, but always inside a 16-byte word that holds at least one byte of the range, so
 // they never touch another page.
 #include <cuda_runtime.h>
@@ -153,25 +154,60 @@ __device__ __forceinline__ Span split_span(unsigned char *dst, const unsigned ch
     return s;
 }
 
+__device__ __forceinline__ uint4 shfl_down1(const uint4 &x, unsigned width) {
+    uint4 r;
+    r.x = __shfl_down_sync(0xffffffffu, x.x, 1, width);
+    r.y = __shfl_down_sync(0xffffffffu, x.y, 1, width);
+    r.z = __shfl_down_sync(0xffffffffu, x.z, 1, width);
+    r.w = __shfl_down_sync(0xffffffffu, x.w, 1, width);
+    return r;
+}
+
+__device__ __forceinline__ uint4 shfl_first(const uint4 &x, unsigned width) {
+    uint4 r;
+    r.x = __shfl_sync(0xffffffffu, x.x, 0, width);
+    r.y = __shfl_sync(0xffffffffu, x.y, 0, width);
+    r.z = __shfl_sync(0xffffffffu, x.z, 0, width);
+    r.w = __shfl_sync(0xffffffffu, x.w, 0, width);
+    return r;
+}
+
+// Loads the body of a span into registers.  Must be called by all 32 lanes of a warp together,
+// with spans of one sub (so `glanes` is the same in every lane): the misaligned case exchanges
+// words between lanes.
+//
+// Misaligned source: destination vector i needs the aligned source words i and i+1.  Word i+1 is
+// what the next lane of the group loads as ITS word for the same j (or, for the last lane of the
+// group, what the first lane loads for j+1), so every lane loads one word per vector (plus one
+// more word per group) and gets the second from a shuffle, instead of loading both.
 __device__ __forceinline__ void load_span(const Span &s, uint4 (&v)[VEC_PER_LANE]) {
-    if (s.shift == 0) {
+    if (!__any_sync(0xffffffffu, s.shift != 0 && s.nvec != 0)) {   // same answer in every lane
         const uint4 *p = reinterpret_cast<const uint4 *>(s.src);
 #pragma unroll
         for (int j = 0; j < VEC_PER_LANE; ++j) {
             const unsigned i = s.glane + s.glanes * j;
             if (i < s.nvec) v[j] = ld_stream(p + i);
         }
-    } else {
-        const uint4 *p = reinterpret_cast<const uint4 *>(s.src - s.shift);
+        return;
+    }
+    // Words to load: 0 .. nvec-1, and word nvec too when this lane's row is misaligned (it then
+    // holds at least one byte of the row, see the note on alignment at the top of the file).
+    const uint4 *p = reinterpret_cast<const uint4 *>(s.src - s.shift);
+    const unsigned words = s.nvec == 0 ? 0u : s.nvec + (s.shift != 0 ? 1u : 0u);
+    uint4 lo[VEC_PER_LANE + 1];
 #pragma unroll
-        for (int j = 0; j < VEC_PER_LANE; ++j) {
-            const unsigned i = s.glane + s.glanes * j;
-            if (i < s.nvec) {
-                const uint4 lo = ld_keep(p + i);
-                const uint4 hi = ld_keep(p + i + 1);
-                v[j] = funnel16(lo, hi, s.shift);
-            }
-        }
+    for (int j = 0; j <= VEC_PER_LANE; ++j) {
+        const unsigned i = s.glane + s.glanes * j;
+        lo[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (i < words) lo[j] = ld_stream(p + i);
+    }
+    const bool last = s.glane + 1u == s.glanes;
+#pragma unroll
+    for (int j = 0; j < VEC_PER_LANE; ++j) {
+        const uint4 from_next_lane = shfl_down1(lo[j], s.glanes);
+        const uint4 from_first_lane = shfl_first(lo[j + 1], s.glanes);
+        const uint4 hi = last ? from_first_lane : from_next_lane;
+        v[j] = s.shift != 0 ? funnel16(lo[j], hi, s.shift) : lo[j];
     }
 }
 
@@ -209,8 +245,8 @@ __device__ __forceinline__ Span open_sub(const GatherOp *ops, unsigned n_ops, ui
             none.dst = nullptr;
             none.nvec = 0;
             none.shift = 0;
-            none.glane = 0;
-            none.glanes = 32;
+            none.glane = lane & (glanes - 1u);
+            none.glanes = glanes;     // the same in every lane of the warp, as load_span needs
             return none;
         }
         return split_span(reinterpret_cast<unsigned char *>(op.dst + row * op.dst_pitch),

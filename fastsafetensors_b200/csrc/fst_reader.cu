@@ -155,7 +155,8 @@ struct Request {
     CUfileHandle_t cf_handle = nullptr;
     uint64_t remaining = 0;   // windows not yet handed to the copy engine / destination
     uint64_t bytes_done = 0;
-    int status = FST_OK;
+    std::atomic<int> status{FST_OK};  // written under the reader's mutex; workers peek at it
+                                       // without the lock to skip the I/O of a failed request
     std::string error;
 };
 
@@ -488,8 +489,8 @@ ssize_t Reader::do_pread(int fd, void *buf, size_t len, off_t off) {
 void Reader::finish(const Task &t, int status, const std::string &err, uint64_t bytes) {
     std::lock_guard<std::mutex> lock(mu_);
     Request &r = *t.req;
-    if (status != FST_OK && r.status == FST_OK) {
-        r.status = status;
+    if (status != FST_OK && r.status.load(std::memory_order_relaxed) == FST_OK) {
+        r.status.store(status, std::memory_order_relaxed);
         r.error = err;
     }
     r.bytes_done += bytes;
@@ -506,7 +507,7 @@ void Reader::run_task(const Task &t, Slot &slot, int worker_index) {
     Request &r = *t.req;
     const bool to_device = cfg_.device >= 0;
     char msg[256];
-    if (r.status != FST_OK) {  // the request already failed: drain without I/O
+    if (r.status.load(std::memory_order_relaxed) != FST_OK) {  // already failed: drain without I/O
         finish(t, FST_OK, "", 0);
         return;
     }

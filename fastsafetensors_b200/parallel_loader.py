@@ -30,6 +30,7 @@ except ImportError:  # pragma: no cover
         return iterable
 
 from . import cpp as fstcpp
+from .common import SingleGroup
 from .loader import BaseSafeTensorsFileLoader, SafeTensorsFileLoader
 
 _BAR_FORMAT = "{desc}: {percentage:3.0f}% Completed | {n_fmt}/{total_fmt} [{elapsed}<{remaining}, {rate_fmt}]\n"
@@ -94,7 +95,9 @@ class PipelineParallel:
                 "batches must be processed in strict order across all ranks."
             )
         self.loader = loader
-        self.pg = loader.pg
+        # the group as the caller passed it (None = single process), as upstream sizes its batches
+        # (parallel_loader.py:150-159); anything with size() and rank() will do
+        self.pg = pg if pg is not None else SingleGroup()
         self.hf_weights_files = hf_weights_files
         self.max_concurrent_producers = max_concurrent_producers
         self.queue_size = queue_size

@@ -130,3 +130,15 @@ def test_auto_loader_reads_its_configuration(case_files, tmp_path, monkeypatch, 
     assert fst.load_config().create_parallel_kwargs() == {"queue_size": -1}
     with pytest.raises(ValueError):
         fst.LoaderConfig(max_concurrent_producers=2)
+
+
+def test_no_group_means_batches_of_one_file():
+    """``pg=None`` is a single process whatever the loader object is (upstream
+    parallel_loader.py:150-159 sizes its batches from the ``pg`` argument)."""
+    from unittest.mock import MagicMock
+
+    from fastsafetensors_b200.parallel_loader import PipelineParallel
+
+    pipeline = PipelineParallel(None, MagicMock(), ["a.safetensors", "b.safetensors"])
+    assert pipeline.weight_files_batches == [["a.safetensors"], ["b.safetensors"]]
+    assert pipeline.need_clone is True

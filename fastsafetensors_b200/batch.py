@@ -371,6 +371,11 @@ class PeerArena:
         return cls._cache[key]
 
     @classmethod
+    def known_unusable(cls, pg, device) -> bool:
+        """True once setting up arenas for this group has failed (on every rank alike)."""
+        return (id(pg.real_pg), device.as_str()) in cls._failed
+
+    @classmethod
     def release_all(cls) -> None:
         """Destroy every cached arena.  Collective per process group (each ends in a barrier)."""
         for arena in list(cls._cache.values()):

@@ -189,7 +189,7 @@ class FilesBufferOnDevice:
         ``"nccl"``, on all ranks together, where peer mapping is refused.
         Default: the ``FST_B200_TRANSPORT`` environment variable, else ``"auto"``.
         """
-        from .batch import PeerArenaUnavailable, PeerShardExchange, ShardExchange
+        from .batch import PeerArena, PeerArenaUnavailable, PeerShardExchange, ShardExchange
 
         world, me = self.pg.size(), self.pg.rank()
         out: Dict[str, TensorBase] = {}
@@ -201,6 +201,8 @@ class FilesBufferOnDevice:
         device = next(l.device for ls in self.rank_loaders.values() for l in ls)
         transport = resolve_transport(transport, world, device)
         fall_back = transport == "auto"
+        if fall_back and PeerArena.known_unusable(self.pg, device):
+            transport = "nccl"      # tried before on this group: all ranks know, nobody asks again
         for names in self._batches(requests, world, max_batch_bytes):
             batch = OrderedDict((n, requests[n]) for n in names)
             ex = None

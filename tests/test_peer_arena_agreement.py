@@ -79,6 +79,7 @@ def _rank(rank, world, port, fail, out_dir):
     nat.lib = fake
     dev = Device.from_str(f"cuda:{rank}")
     result = {}
+    assert batch.PeerArena.known_unusable(PG(), dev) is False
     try:
         arena = batch.PeerArena.for_group(PG(), 1 << 20, dev)
         result["ok"] = True
@@ -91,6 +92,7 @@ def _rank(rank, world, port, fail, out_dir):
         # not tried again for this group, and without any collective
         with pytest.raises(batch.PeerArenaUnavailable):
             batch.PeerArena.for_group(PG(), 1 << 20, dev)
+        assert batch.PeerArena.known_unusable(PG(), dev) is True
     result["leaked"] = sorted(fake.created | fake.opened)
     dist.barrier()                       # both ranks are still in step
     with open(os.path.join(out_dir, f"r{rank}.json"), "w") as f:

@@ -405,7 +405,7 @@ def b200_arm(args) -> dict:
         read_s = (cpp.get_cpp_metrics().read_ns - r0) / 1e9 / len(times)
         return {"value": round(data_bytes / mean / GB, 3), "unit": "GB/s",
                 "h2d_bytes_per_step": int(data_bytes), "d2h_bytes_per_step": d2h,
-                "s_per_step": round(mean, 4), "steps": steps,
+                "s_per_step": round(mean, 4), "steps": steps, "warmup": warmup,
                 "page_cache": "dropped before every step" if cold else "warm",
                 "rank0_phases_s": {"open_and_headers": round(sum(p[0] for p in parts) / len(parts), 4),
                                    "copy_files_to_device": round(sum(p[1] for p in parts) / len(parts), 4),
@@ -419,7 +419,7 @@ def b200_arm(args) -> dict:
         note("end-to-end phase, cold")
         mA = cpp.get_cpp_metrics()
         if not args.warm_only:
-            result["e2e"] = e2e_phase(True, args.steps, 1)
+            result["e2e"] = e2e_phase(True, args.steps, min(3, max(1, args.warmup)))
             mB = cpp.get_cpp_metrics()
             result["e2e"]["io"] = {"direct_requests": mB.direct_io_requests - mA.direct_io_requests,
                                    "buffered_requests": mB.buffered_io_requests - mA.buffered_io_requests}
@@ -428,7 +428,7 @@ def b200_arm(args) -> dict:
             read_into_page_cache(paths)
         barrier()
         mC = cpp.get_cpp_metrics()
-        result["e2e_warm"] = e2e_phase(False, min(args.steps, 3), 1)
+        result["e2e_warm"] = e2e_phase(False, min(args.steps, 3), 3)
         mD = cpp.get_cpp_metrics()
         result["e2e_warm"]["io"] = {"direct_requests": mD.direct_io_requests - mC.direct_io_requests,
                                     "buffered_requests": mD.buffered_io_requests - mC.buffered_io_requests}

@@ -535,6 +535,12 @@ def storage_roofline(paths, my_paths, rank, barrier, max_over_ranks) -> dict:
 REF_DIR = os.path.join(ROOT, "oracle", "_ref")
 
 
+def _numa_nodes() -> int:
+    import glob
+
+    return max(1, len(glob.glob("/sys/devices/system/node/node[0-9]*")))
+
+
 def _reference_settings(kind: str, paths, world: int):
     """Keyword arguments for upstream's loader and for its ``copy_files_to_device``.
 
@@ -703,7 +709,8 @@ def cpu_baseline(spec, paths, tp: int) -> dict:
                       f"once warm ({warm:.2f} s); the faster of library defaults (one request per "
                       f"file) and the rule of upstream's perf tool (a block per thread), cold GB/s: "
                       f"{t['settings']['tried_gbs']}, used: {t['settings']['used']} {t['settings']['kwargs']}",
-            "warm_value": round(spec.data_bytes / warm / GB, 3), "settings": t["settings"]}
+            "warm_value": round(spec.data_bytes / warm / GB, 3), "settings": t["settings"],
+            "numa_nodes": _numa_nodes()}
 
 
 def reference_cuda_subprocess(args) -> dict:
@@ -756,7 +763,7 @@ def reference_arm(args) -> dict:
         "config": {"workload": f"{spec.name} ({args.scale}): {len(spec.tensors)} tensors, {len(paths)} files, "
                                f"{spec.data_bytes} data bytes, tensor-parallel {tp}-way, host memory", "tp": tp},
         "cpu_baseline": {"value": v, "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference",
-                         "sample": sample},
+                         "sample": sample, "numa_nodes": _numa_nodes(), "settings": t["settings"]},
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                 "page_cache": "dropped before every step"},
         "e2e_warm": {"value": round(rate(t["warm"]), 3), "unit": "GB/s", "files": t["warm"]["files"]},

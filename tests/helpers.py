@@ -26,3 +26,12 @@ def digest_bytes(raw: np.ndarray) -> str:
 def tensor_bytes(t) -> np.ndarray:
     t = t.get_raw() if hasattr(t, "get_raw") else t
     return t.detach().contiguous().reshape(-1).view(torch.uint8).cpu().numpy()
+
+
+def free_port() -> int:
+    """A TCP port that is free on 127.0.0.1 right now, for a test's process-group rendezvous."""
+    import socket
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]

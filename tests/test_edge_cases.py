@@ -12,6 +12,7 @@ from safetensors.torch import load_file, save_file
 
 import fastsafetensors_b200 as fst
 from oracle import st_oracle
+from tests.helpers import free_port
 
 
 def _empty_mix(path: str) -> dict:
@@ -167,11 +168,11 @@ def _run_two_ranks(tmp_path, backend, port):
 
 
 def test_two_gloo_ranks_with_empty_tensors(tmp_path):
-    _run_two_ranks(tmp_path, "gloo", 29871)
+    _run_two_ranks(tmp_path, "gloo", free_port())
 
 
 @pytest.mark.gpu
 def test_two_nccl_ranks_with_empty_tensors(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    _run_two_ranks(tmp_path, "nccl", 29872)
+    _run_two_ranks(tmp_path, "nccl", free_port())

@@ -9,6 +9,7 @@ import torch.multiprocessing as mp
 
 from tests.golden import cases
 from tests.test_multi_cpu import _all_keys_rank, _rank_main
+from tests.helpers import free_port
 
 pytestmark = pytest.mark.gpu
 MULTI = [c for c in cases.CASES if c["world"] > 1]
@@ -23,7 +24,7 @@ def test_nccl_ranks_match_upstream(case, batched, golden, case_files, tmp_path):
     if batched and case["steps"][0][0] != "plan":
         pytest.skip("as_dict in the per-tensor run already goes through the batched exchange")
     paths = case_files(case)
-    port = 29900 + 3 * cases.CASES.index(case) + [False, "nccl", "peer"].index(batched)
+    port = free_port()
     mp.spawn(_rank_main, args=(world, case, paths, port, str(tmp_path), bool(batched), "nccl", batched or "nccl"),
              nprocs=world, join=True)
     for rank in range(world):
@@ -41,7 +42,7 @@ def test_every_key_access_over_nccl(case_files, tmp_path):
 
     case = [c for c in cases.CASES if c["id"] == "llama3_8b_w2_cols"][0]
     paths = sorted(case_files(case))[:2]
-    mp.spawn(_all_keys_rank, args=(2, paths, 29996, str(tmp_path), "nccl"), nprocs=2, join=True)
+    mp.spawn(_all_keys_rank, args=(2, paths, free_port(), str(tmp_path), "nccl"), nprocs=2, join=True)
     want = {}
     for p in paths:
         fo = st_oracle.FileOracle(p)

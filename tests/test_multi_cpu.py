@@ -12,6 +12,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from tests.golden import cases
+from tests.helpers import free_port
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -83,7 +84,7 @@ def test_gloo_ranks_match_upstream(case, batched, golden, case_files, tmp_path):
         pytest.skip("as_dict in the per-tensor run already goes through the batched exchange")
     paths = case_files(case)
     world = case["world"]
-    port = 29700 + 2 * cases.CASES.index(case) + int(batched)
+    port = free_port()
     mp.spawn(_rank_main, args=(world, case, paths, port, str(tmp_path), batched), nprocs=world, join=True)
     for rank in range(world):
         got = json.load(open(tmp_path / f"rank{rank}.json"))
@@ -155,7 +156,7 @@ def test_packed_and_8bit_float_dtypes_shard_as_bytes(tmp_path):
     path = str(tmp_path / "packed.safetensors")
     _write_packed(path)
     world = 2
-    mp.spawn(_packed_rank, args=(world, path, 29990, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_packed_rank, args=(world, path, free_port(), str(tmp_path)), nprocs=world, join=True)
     fo = st_oracle.FileOracle(path)
     for rank in range(world):
         got = json.load(open(tmp_path / f"rank{rank}.json"))
@@ -214,7 +215,7 @@ def test_asking_for_every_key_switches_to_one_broadcast_per_file(case_files, tmp
 
     case = [c for c in cases.CASES if c["id"] == "llama3_8b_w2_cols"][0]
     paths = sorted(case_files(case))[:2]
-    mp.spawn(_all_keys_rank, args=(2, paths, 29995, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_all_keys_rank, args=(2, paths, free_port(), str(tmp_path)), nprocs=2, join=True)
     want = {}
     for p in paths:
         fo = st_oracle.FileOracle(p)

@@ -16,6 +16,7 @@ from fastsafetensors_b200.frameworks import get_framework_op
 from oracle import st_oracle
 from tests.golden import cases
 from tests.helpers import digest_bytes, digest_tensor
+from tests.helpers import free_port
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CASE = [c for c in cases.CASES if c["id"] == "llama3_70b_w8"][0]   # 30 small files
@@ -101,7 +102,7 @@ def _rank_main(rank, world, paths, port, out_dir, queue_size):
 def test_two_ranks_every_rank_gets_every_tensor(queue_size, case_files, tmp_path):
     paths = sorted(case_files(CASE))[:7]          # odd count: the last batch has one file only
     want = {k: list(v) for k, v in _expected(paths).items()}
-    mp.spawn(_rank_main, args=(2, paths, 29950 + queue_size, str(tmp_path), queue_size), nprocs=2, join=True)
+    mp.spawn(_rank_main, args=(2, paths, free_port(), str(tmp_path), queue_size), nprocs=2, join=True)
     for rank in range(2):
         got = json.load(open(tmp_path / f"rank{rank}.json"))
         assert got == want, rank

@@ -10,6 +10,7 @@ import sys
 import pytest
 import torch.distributed as dist
 import torch.multiprocessing as mp
+from tests.helpers import free_port
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -103,7 +104,7 @@ def _rank(rank, world, port, fail, out_dir):
 @pytest.mark.parametrize("fail", [None, (0, "create"), (1, "export"), (1, "open"), (0, "open")],
                          ids=lambda f: "ok" if f is None else f"rank{f[0]}_{f[1]}")
 def test_both_ranks_agree(fail, tmp_path):
-    port = 29900 + (0 if fail is None else 1 + 2 * fail[0] + ["create", "export", "open"].index(fail[1]))
+    port = free_port()
     mp.spawn(_rank, args=(2, port, fail, str(tmp_path)), nprocs=2, join=True)
     got = [json.load(open(tmp_path / f"r{r}.json")) for r in range(2)]
     assert got[0]["leaked"] == [] and got[1]["leaked"] == []

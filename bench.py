@@ -674,7 +674,11 @@ def run_reference(spec, paths, tp: int, phases, timeout_s: float = 900.0, settin
     plan_items = list(plan_for(spec, tp).items())
     with tempfile.TemporaryDirectory() as tmp:
         out_path = os.path.join(tmp, "times.json")
-        port = 29800 + os.getpid() % 100
+        import socket
+
+        with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:   # a port that is free now
+            sock.bind(("127.0.0.1", 0))
+            port = sock.getsockname()[1]
         if tp == 1:
             _reference_rank(0, 1, paths, plan_items, phases, port, out_path, settings)
         else:

@@ -145,7 +145,7 @@ def load_spec(args):
     """The checkpoint spec of the run; ``--layers L`` cuts it to the first L layers."""
     import re
 
-    from fastsafetensors_b200 import synth
+    from tests import synth
 
     spec = synth.config(args.config, args.scale)
     if args.layers > 0:
@@ -158,7 +158,7 @@ def load_spec(args):
 
 
 def prepare_files(spec, directory: str, rank: int, barrier) -> list:
-    from fastsafetensors_b200 import synth
+    from tests import synth
 
     out = os.path.join(directory, f"{spec.name}")
     if rank == 0:
@@ -180,7 +180,8 @@ def b200_arm(args) -> dict:
 
     import fastsafetensors_b200 as fst
     from fastsafetensors_b200 import _native as nat
-    from fastsafetensors_b200 import cpp, synth
+    from fastsafetensors_b200 import cpp
+    from tests import synth
     from fastsafetensors_b200.batch import PeerArenaUnavailable, PeerShardExchange, ShardExchange
     from fastsafetensors_b200.file_buffer import resolve_transport
 
@@ -507,7 +508,8 @@ def storage_roofline(paths, my_paths, rank, barrier, max_over_ranks) -> dict:
     """Cold O_DIRECT read bandwidth of the same files with the same thread count, into host
     memory (the role fio plays where it is installed): the ceiling for a cold end-to-end load."""
     from fastsafetensors_b200 import _native as nat
-    from fastsafetensors_b200 import cpp, synth
+    from fastsafetensors_b200 import cpp
+    from tests import synth
     import numpy as np
 
     if rank == 0:
@@ -573,7 +575,7 @@ def _reference_rank(rank: int, world: int, paths, plan_items, phases, port: int,
     import torch.distributed as dist
 
     import fastsafetensors as ref
-    from fastsafetensors_b200 import synth
+    from tests import synth
 
     torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
     pg = None
@@ -730,7 +732,7 @@ def reference_cuda_subprocess(args) -> dict:
 
 
 def reference_arm(args) -> dict:
-    from fastsafetensors_b200 import synth
+    from tests import synth
 
     rank, _, world = dist_env()
     if rank != 0:
@@ -783,7 +785,7 @@ def reference_cuda_arm(args) -> dict:
     import torch
 
     import fastsafetensors as ref
-    from fastsafetensors_b200 import synth
+    from tests import synth
 
     spec = load_spec(args)
     paths = prepare_files(spec, args.dir, 0, lambda: None)

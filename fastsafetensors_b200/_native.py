@@ -24,7 +24,7 @@ from typing import Sequence, Tuple
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libfst_b200.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # status codes of include/fst_b200.h
 OK, EINVAL, ERANGE, ENOCUDA, ECUDA, EIO, ETIMEOUT, ENOMEM, ELIMIT, EGDS = (
@@ -44,7 +44,8 @@ EXPORTS = (
     "fst_reader_inject_fault", "fst_gather", "fst_gather_static", "fst_gather_host",
     "fst_realign", "fst_release_workspaces", "fst_arena_create", "fst_arena_export",
     "fst_arena_open_peer", "fst_arena_close_peer", "fst_arena_destroy", "fst_convert",
-    "fst_cufile_available", "fst_gds_supported",
+    "fst_cufile_available", "fst_gds_supported", "fst_reader_order_after", "fst_device_alloc",
+    "fst_device_free", "fst_memcpy_h2d_async",
 )
 
 
@@ -138,6 +139,12 @@ def _load() -> ctypes.CDLL:
     ]
     lib.fst_reader_wait.argtypes = [c_uint64, c_int64, c_int64, POINTER(c_uint64)]
     lib.fst_reader_destroy.argtypes = [c_uint64]
+    lib.fst_reader_order_after.argtypes = [c_uint64, c_uint64]
+    lib.fst_device_alloc.argtypes = [c_uint64]
+    lib.fst_device_alloc.restype = c_uint64
+    lib.fst_device_free.argtypes = [c_uint64]
+    lib.fst_device_free.restype = None
+    lib.fst_memcpy_h2d_async.argtypes = [c_uint64, c_uint64, c_uint64]
     lib.fst_reader_inject_fault.argtypes = [c_uint64, c_int64, c_int, c_int64]
     lib.fst_gather.argtypes = [
         POINTER(Copy2D), c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64,

@@ -47,6 +47,11 @@ class B200FileCopier(CopierInterface):
         total = meta.size_bytes - meta.header_length
         gbuf = self.framework.alloc_tensor_memory(total, self.device)
         try:
+            if self.device.type != DeviceType.CPU:
+                # the image comes from torch's stream-ordered allocator: its memory may have
+                # belonged to an image that a gather or a collective queued on the current stream
+                # still reads, so the reader's own copy streams must queue behind that stream
+                self.reader.order_after(self.framework.current_stream(self.device))
             self.request = self.reader.submit(meta.src, meta.header_length, total, gbuf, 0)
         except Exception:
             self.framework.free_tensor_memory(gbuf, self.device)
@@ -113,8 +118,11 @@ class B200FileCopier(CopierInterface):
         nat.convert(convert_ops, stream)
         nat.gather(copy_ops, stream)
         tensors.clear()
-        self.framework.free_tensor_memory(gbuf, self.device)   # the launches above are ordered
-        gbuf.adopt(new)                                        # before any reuse of that memory
+        # The launches above still read the old image.  Releasing it now is safe: torch hands
+        # the memory only to later allocations of the same stream, and whoever writes it from
+        # another stream orders itself behind this one first (submit_io does, for the reader).
+        self.framework.free_tensor_memory(gbuf, self.device)
+        gbuf.adopt(new)
         return out
 
 

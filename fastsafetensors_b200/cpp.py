@@ -130,6 +130,11 @@ class Reader:
         )
         return req.value
 
+    def order_after(self, stream: int) -> None:
+        """Order the reader's copies behind the work queued so far on ``stream`` (a
+        ``cudaStream_t`` as an integer); see ``fst_reader_order_after``."""
+        nat.check(nat.lib.fst_reader_order_after(self._handle, stream), "fst_reader_order_after")
+
     def wait(self, request: int, timeout_ms: int = -1) -> int:
         done = c_uint64(0)
         nat.check(nat.lib.fst_reader_wait(self._handle, request, timeout_ms, byref(done)),
@@ -307,6 +312,22 @@ def cpu_malloc(length: int) -> int:
 
 def cpu_free(addr: int) -> None:
     nat.lib.fst_host_free(addr)
+
+
+def gpu_malloc(length: int) -> int:
+    """``cudaMalloc`` on the current device; 0 on failure (ext.cpp:559-565)."""
+    return int(nat.lib.fst_device_alloc(length))
+
+
+def gpu_free(addr: int) -> None:
+    nat.lib.fst_device_free(addr)
+
+
+def memcpy_h2d_async(dst: int, src: int, size: int) -> int:
+    """``cudaMemcpyAsync`` host -> device on the default stream; returns the CUDA error code,
+    -1 without a CUDA device (ext.cpp:959-971)."""
+    rc = int(nat.lib.fst_memcpy_h2d_async(dst, src, size))
+    return -1 if rc == nat.ENOCUDA else rc
 
 
 def load_library_functions(cudart_lib_name: str = "") -> None:

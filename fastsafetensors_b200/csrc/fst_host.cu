@@ -93,6 +93,39 @@ extern "C" int fst_cuda_device_count(void) {
 
 extern "C" void fst_set_debug(int on) { g_debug.store(on ? 1 : 0); }
 
+extern "C" uint64_t fst_device_alloc(uint64_t nbytes) {
+    clear_error();
+    if (!cuda_usable()) {
+        set_error("fst_device_alloc: no CUDA device");
+        return 0;
+    }
+    void *p = nullptr;
+    const cudaError_t e = cudaMalloc(&p, nbytes);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        set_error("fst_device_alloc: cudaMalloc(%llu) failed: %s", (unsigned long long)nbytes,
+                  cudaGetErrorString(e));
+        return 0;
+    }
+    return (uint64_t)(uintptr_t)p;
+}
+
+extern "C" void fst_device_free(uint64_t addr) {
+    if (addr != 0 && cuda_usable()) cudaFree((void *)(uintptr_t)addr);
+}
+
+extern "C" int fst_memcpy_h2d_async(uint64_t dst, uint64_t src, uint64_t nbytes) {
+    clear_error();
+    if (!cuda_usable()) {
+        set_error("fst_memcpy_h2d_async: no CUDA device");
+        return FST_ENOCUDA;
+    }
+    const cudaError_t e = cudaMemcpyAsync((void *)(uintptr_t)dst, (const void *)(uintptr_t)src,
+                                          nbytes, cudaMemcpyHostToDevice, nullptr);
+    if (e != cudaSuccess) (void)cudaGetLastError();
+    return (int)e;
+}
+
 extern "C" int fst_device_pci_bus(int device, char *out, int n) {
     clear_error();
     if (out == nullptr || n < 16) {

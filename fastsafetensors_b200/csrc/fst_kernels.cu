@@ -492,8 +492,20 @@ int check_ops(const fst_copy2d_t *ops, uint64_t n, uint64_t src_base, uint64_t s
             set_error("fst_gather: op %llu: row_bytes too large", (unsigned long long)i);
             return FST_ELIMIT;
         }
-        const uint64_t s_end = c.src + (c.rows - 1) * c.src_pitch + c.row_bytes;
-        const uint64_t d_end = c.dst + (c.rows - 1) * c.dst_pitch + c.row_bytes;
+        // end addresses, refusing anything that wraps around 2^64 (a wrapped end would slip
+        // past the range checks below)
+        uint64_t s_end = 0, d_end = 0;
+        if (__builtin_mul_overflow(c.rows - 1, c.src_pitch, &s_end) ||
+            __builtin_add_overflow(s_end, c.row_bytes, &s_end) ||
+            __builtin_add_overflow(s_end, c.src, &s_end) ||
+            __builtin_mul_overflow(c.rows - 1, c.dst_pitch, &d_end) ||
+            __builtin_add_overflow(d_end, c.row_bytes, &d_end) ||
+            __builtin_add_overflow(d_end, c.dst, &d_end) ||
+            (src_len && src_base + src_len < src_base) || (dst_len && dst_base + dst_len < dst_base)) {
+            set_error("fst_gather: op %llu: address arithmetic overflows 64 bits",
+                      (unsigned long long)i);
+            return FST_ERANGE;
+        }
         if (src_len && (c.src < src_base || s_end > src_base + src_len)) {
             set_error("fst_gather: op %llu reads [%#llx,%#llx) outside the source buffer "
                       "[%#llx,%#llx)", (unsigned long long)i, (unsigned long long)c.src,
@@ -693,6 +705,10 @@ static __device__ __align__(256) GatherOp g_static_table[FST_GATHER_STATIC_MAX_O
 // address of the table per device (looked up once, with that device current).
 GatherOp g_static_host[FST_GATHER_STATIC_MAX_OPS];
 GatherOp *g_static_dev[MAX_DEVICES];
+// Guards the host twin and the address cache.  Its own lock, not the workspace's: the table
+// upload below can stall the calling thread until earlier work on the stream is done, and
+// fst_gather callers on other threads must not queue behind that.
+std::mutex g_static_mutex;
 
 }  // namespace
 }  // namespace fst
@@ -724,8 +740,7 @@ extern "C" int fst_gather_static(const fst_copy2d_t *ops, uint64_t n_ops, uint64
         set_error("fst_gather_static: device index %d not supported", dev);
         return FST_ELIMIT;
     }
-    // one lock for the shared host twin, the per-device address cache and the grid-size cache
-    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
     if (g_static_dev[dev] == nullptr) {
         GatherOp *p = nullptr;
         const cudaError_t e = cudaGetSymbolAddress((void **)&p, g_static_table);

@@ -54,21 +54,34 @@ struct CuFileApi {
     ssize_t (*Read)(CUfileHandle_t, void *, size_t, off_t, off_t) = nullptr;
     bool loaded = false;
     bool tried = false;
+    bool stand_in = false;  // a test double that needs neither the cuFile driver nor nvidia-fs
     int driver_users = 0;
 };
 CuFileApi g_cufile;
 std::mutex g_cufile_mutex;
 
+// FST_B200_CUFILE_LIB names a library to load in place of libcufile.so.  It is meant for a
+// host-side double of the seven entry points (tests run the cuFile code path through one, as
+// upstream runs its own through a table of fakes, ext.cpp:126-196).  A library counts as such a
+// double only if it also exports the marker symbol `fst_cufile_stand_in`; for anything else the
+// nvidia-fs check of cufile_acquire() still applies, so the variable cannot be used to walk the
+// real library into a host on which it cannot work.
 bool load_cufile_locked() {
     if (g_cufile.tried) return g_cufile.loaded;
     g_cufile.tried = true;
     void *h = nullptr;
-    for (const char *name : {"libcufile.so.0", "libcufile.so"}) {
-        h = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
-        if (h) break;
+    const char *named = std::getenv("FST_B200_CUFILE_LIB");
+    if (named && named[0]) {
+        h = dlopen(named, RTLD_NOW | RTLD_LOCAL);
+    } else {
+        for (const char *name : {"libcufile.so.0", "libcufile.so"}) {
+            h = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+            if (h) break;
+        }
     }
     if (!h) return false;
     auto sym = [&](const char *n) { return dlsym(h, n); };
+    g_cufile.stand_in = sym("fst_cufile_stand_in") != nullptr;
     g_cufile.DriverOpen = (decltype(g_cufile.DriverOpen))sym("cuFileDriverOpen");
     g_cufile.DriverClose = (decltype(g_cufile.DriverClose))sym("cuFileDriverClose");
     g_cufile.HandleRegister = (decltype(g_cufile.HandleRegister))sym("cuFileHandleRegister");
@@ -84,8 +97,24 @@ bool load_cufile_locked() {
 // Opens the cuFile driver for one more user.  Returns FST_OK or FST_EGDS (error text set).
 int cufile_acquire() {
     std::lock_guard<std::mutex> lock(g_cufile_mutex);
+    // Without the nvidia-fs module cuFile could only run in its compatibility mode, and on hosts
+    // that also lack a udev database cuFileDriverOpen() has been seen never to return.  Such a
+    // host gets the error a caller retries on (vLLM looks for "gds" in the text and loads again
+    // with nogds=True) instead of a call that may hang; libcufile is not even loaded.
+    const char *named = std::getenv("FST_B200_CUFILE_LIB");
+    const bool substitute = named && named[0];
+    if (!substitute && fst_gds_supported(0) == 0) {
+        set_error("gds: the nvidia-fs kernel module is not loaded; cuFile's compatibility mode "
+                  "is not used");
+        return FST_EGDS;
+    }
     if (!load_cufile_locked()) {
-        set_error("gds: libcufile.so could not be loaded");
+        set_error("gds: %s could not be loaded", substitute ? named : "libcufile.so");
+        return FST_EGDS;
+    }
+    if (!g_cufile.stand_in && fst_gds_supported(0) == 0) {  // a named library that is no double
+        set_error("gds: the nvidia-fs kernel module is not loaded; cuFile's compatibility mode "
+                  "is not used");
         return FST_EGDS;
     }
     if (g_cufile.driver_users == 0) {
@@ -190,7 +219,9 @@ class Reader {
         fault_err_ = err;
         fault_short_ = short_bytes;
         reads_seen_ = 0;
+        fault_armed_.store(nth > 0, std::memory_order_release);
     }
+    int order_after(uint64_t stream);
     void shutdown();
 
   private:
@@ -226,8 +257,13 @@ class Reader {
     int64_t next_id_ = 1;
     int64_t fault_nth_ = 0, fault_short_ = -1, reads_seen_ = 0;
     int fault_err_ = 0;
+    std::atomic<bool> fault_armed_{false};
+    cudaEvent_t order_event_ = nullptr;  // see order_after
 };
 
+// Creates what the first submit needs.  Every resource is created at most once: a call that
+// failed halfway (a stream or an event could not be made) is picked up where it stopped by the
+// next call instead of creating the earlier resources a second time.
 int Reader::start() {
     if (started_) return FST_OK;
     const int nslots = cfg_.threads * cfg_.slots_per_thread;
@@ -237,45 +273,85 @@ int Reader::start() {
             set_error("reader: cudaSetDevice(%d) failed: %s", cfg_.device, cudaGetErrorString(e));
             return FST_ECUDA;
         }
-        streams_.resize(cfg_.copy_streams);
-        for (auto &s : streams_) {
+        while ((int)streams_.size() < cfg_.copy_streams) {
+            cudaStream_t s = nullptr;
             e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
             if (e != cudaSuccess) {
+                (void)cudaGetLastError();
                 set_error("reader: cudaStreamCreate failed: %s", cudaGetErrorString(e));
+                return FST_ECUDA;
+            }
+            streams_.push_back(s);
+        }
+        if (order_event_ == nullptr) {
+            e = cudaEventCreateWithFlags(&order_event_, cudaEventDisableTiming);
+            if (e != cudaSuccess) {
+                (void)cudaGetLastError();
+                order_event_ = nullptr;
+                set_error("reader: cudaEventCreate failed: %s", cudaGetErrorString(e));
                 return FST_ECUDA;
             }
         }
     }
-    slots_.resize(nslots);
+    if ((int)slots_.size() != nslots) slots_.resize(nslots);
     if (cfg_.device >= 0) {
         for (int i = 0; i < nslots; ++i) {
+            if (slots_[i].done != nullptr) continue;
             const cudaError_t e = cudaEventCreateWithFlags(&slots_[i].done, cudaEventDisableTiming);
             if (e != cudaSuccess) {
+                (void)cudaGetLastError();
+                slots_[i].done = nullptr;
                 set_error("reader: cudaEventCreate failed: %s", cudaGetErrorString(e));
                 return FST_ECUDA;
             }
         }
         if (cfg_.io_mode == FST_IO_CUFILE) {
             // cuFile lands file windows in the device staging ring directly; no host ring
-            int rc = cufile_acquire();
-            if (rc != FST_OK) return rc;
-            cufile_open_ = true;
-            rc = ensure_stage_ring();
+            if (!cufile_open_) {
+                const int rc = cufile_acquire();
+                if (rc != FST_OK) return rc;
+                cufile_open_ = true;
+            }
+            const int rc = ensure_stage_ring();
             if (rc != FST_OK) {
                 set_error("gds: device staging ring allocation failed");
                 return rc;
             }
-            FST_DEBUG("cufile: registering the staging ring");
-            const CUfileError_t e2 = g_cufile.BufRegister(stage_ring_, stage_bytes_, 0);
-            stage_registered_ = e2.err == CU_FILE_SUCCESS;  // unregistered buffers still work
-            FST_DEBUG("reader: cuFile staging ring of %llu bytes, registered=%d",
-                      (unsigned long long)stage_bytes_, (int)stage_registered_);
+            if (!stage_registered_) {
+                FST_DEBUG("cufile: registering the staging ring");
+                const CUfileError_t e2 = g_cufile.BufRegister(stage_ring_, stage_bytes_, 0);
+                stage_registered_ = e2.err == CU_FILE_SUCCESS;  // unregistered buffers still work
+                FST_DEBUG("reader: cuFile staging ring of %llu bytes, registered=%d",
+                          (unsigned long long)stage_bytes_, (int)stage_registered_);
+            }
         }
     }
     worker_ring_.assign(cfg_.threads, nullptr);
     ring_pinned_ = cfg_.device >= 0;
     started_ = true;
     for (int i = 0; i < cfg_.threads; ++i) threads_.emplace_back(&Reader::worker, this, i);
+    return FST_OK;
+}
+
+// Orders everything this reader copies from now on behind the work queued so far on `stream`.
+// A destination buffer that comes from a stream-ordered allocator (torch's caching allocator)
+// may still be read by kernels queued on the allocating stream under its previous owner; the
+// reader writes through its own non-blocking copy streams, which know nothing of that stream
+// unless told.  One event is recorded on `stream` and every copy stream waits for it.
+int Reader::order_after(uint64_t stream) {
+    if (cfg_.device < 0) return FST_OK;
+    std::lock_guard<std::mutex> lock(mu_);
+    const int rc = start();
+    if (rc != FST_OK) return rc;
+    cudaError_t e = cudaEventRecord(order_event_, (cudaStream_t)stream);
+    for (size_t i = 0; e == cudaSuccess && i < streams_.size(); ++i)
+        e = cudaStreamWaitEvent(streams_[i], order_event_, 0);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        set_error("reader: ordering the copy streams behind stream %#llx failed: %s",
+                  (unsigned long long)stream, cudaGetErrorString(e));
+        return FST_ECUDA;
+    }
     return FST_OK;
 }
 
@@ -344,6 +420,8 @@ void Reader::shutdown() {
     for (auto &s : slots_)
         if (s.done) cudaEventDestroy(s.done);
     slots_.clear();
+    if (order_event_) cudaEventDestroy(order_event_);
+    order_event_ = nullptr;
     if (stage_registered_) g_cufile.BufDeregister(stage_ring_);
     stage_registered_ = false;
     if (stage_ring_) cudaFree(stage_ring_);
@@ -469,10 +547,12 @@ int Reader::submit(const char *path, uint64_t file_off, uint64_t nbytes, uint64_
 }
 
 ssize_t Reader::do_pread(int fd, void *buf, size_t len, off_t off) {
-    {
+    // the injector is for tests: the hot loop only looks at one relaxed flag unless it is armed
+    if (fault_armed_.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(mu_);
         if (fault_nth_ > 0 && ++reads_seen_ == fault_nth_) {
             fault_nth_ = 0;
+            fault_armed_.store(false, std::memory_order_release);
             if (fault_short_ >= 0) {
                 len = (size_t)std::min<int64_t>((int64_t)len, fault_short_);
                 if (len == 0) return 0;
@@ -674,6 +754,9 @@ void Reader::worker(int index) {
     }
 }
 
+// The request stays registered until its copies have been drained: a wait that runs out of time
+// (in either phase) can be repeated with the same id, and the request's own status and error text
+// are still there when it finally completes.
 int Reader::wait(int64_t id, int64_t timeout_ms, uint64_t *bytes_done) {
     std::shared_ptr<Request> req;
     const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
@@ -693,9 +776,9 @@ int Reader::wait(int64_t id, int64_t timeout_ms, uint64_t *bytes_done) {
                       (long long)id, (unsigned long long)req->remaining, (long long)timeout_ms);
             return FST_ETIMEOUT;
         }
-        requests_.erase(it);
     }
     if (bytes_done) *bytes_done = req->bytes_done;
+    int rc = FST_OK;
     if (cfg_.device >= 0) {
         // every window was enqueued; drain the copy streams (bounded when a timeout was given)
         for (auto &s : streams_) {
@@ -707,17 +790,23 @@ int Reader::wait(int64_t id, int64_t timeout_ms, uint64_t *bytes_done) {
                     if (std::chrono::steady_clock::now() > deadline) {
                         set_error("reader: copies of request %lld not complete after %lld ms",
                                   (long long)id, (long long)timeout_ms);
-                        return FST_ETIMEOUT;
+                        return FST_ETIMEOUT;  // still registered: the caller may wait again
                     }
                     std::this_thread::sleep_for(std::chrono::microseconds(50));
                 }
             }
             if (e != cudaSuccess) {
                 set_error("reader: copy stream failed: %s", cudaGetErrorString(e));
-                return FST_ECUDA;
+                rc = FST_ECUDA;
+                break;
             }
         }
     }
+    {
+        std::lock_guard<std::mutex> lock(mu_);
+        requests_.erase(id);
+    }
+    if (rc != FST_OK) return rc;
     if (req->status != FST_OK) {
         set_error("reader: request %lld failed: %s", (long long)id, req->error.c_str());
         return req->status;
@@ -796,6 +885,16 @@ extern "C" int fst_reader_wait(uint64_t reader, int64_t request, int64_t timeout
         return FST_EINVAL;
     }
     return r->wait(request, timeout_ms, bytes_done);
+}
+
+extern "C" int fst_reader_order_after(uint64_t reader, uint64_t stream) {
+    clear_error();
+    Reader *r = lookup(reader);
+    if (r == nullptr) {
+        set_error("fst_reader_order_after: bad handle");
+        return FST_EINVAL;
+    }
+    return r->order_after(stream);
 }
 
 extern "C" int fst_reader_destroy(uint64_t reader) {

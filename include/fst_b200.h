@@ -31,7 +31,7 @@ extern "C" {
 #pragma GCC visibility push(default) /* the library itself is built with hidden visibility */
 #endif
 
-#define FST_B200_ABI_VERSION 1
+#define FST_B200_ABI_VERSION 2
 
 /* status codes */
 #define FST_OK 0
@@ -80,6 +80,16 @@ int fst_pin_numa(int node);
 uint64_t fst_host_alloc(uint64_t nbytes);
 void fst_host_free(uint64_t addr);
 
+/* Plain device allocation and release on the current device (cudaMalloc / cudaFree); 0 on
+ * failure.  Replaces gpu_malloc()/gpu_free() (ext.cpp:559-569).  The loader itself does not use
+ * them (its images are torch allocations); they exist for callers of upstream's module API. */
+uint64_t fst_device_alloc(uint64_t nbytes);
+void fst_device_free(uint64_t addr);
+
+/* cudaMemcpyAsync host -> device of nbytes on the legacy default stream; returns the CUDA error
+ * code (0 = success), or FST_ENOCUDA.  Replaces memcpy_h2d_async() (ext.cpp:959-971). */
+int fst_memcpy_h2d_async(uint64_t dst, uint64_t src, uint64_t nbytes);
+
 /* Copy nbytes of HOST memory at addr into out.  Replaces read_buffer() (ext.cpp:535-540). */
 int fst_read_host(uint64_t addr, uint64_t nbytes, void *out);
 
@@ -126,7 +136,9 @@ int fst_get_metrics(fst_metrics_t *out);
 #define FST_IO_DIRECT 1   /* O_DIRECT; falls back to buffered if the filesystem refuses it   */
 #define FST_IO_BUFFERED 2 /* plain pread through the page cache                              */
 #define FST_IO_CUFILE 3   /* cuFileRead into the registered device staging ring (device dst only);
-                             FST_EGDS, with "gds" in the error text, when cuFile cannot be used  */
+                             FST_EGDS, with "gds" in the error text, when cuFile cannot be used:
+                             no libcufile, or no nvidia-fs module (checked BEFORE the cuFile
+                             driver is opened; its compatibility mode is never entered)          */
 
 typedef struct fst_reader_config {
     int32_t device;           /* CUDA device of destinations; -1: destinations are host memory */
@@ -155,9 +167,18 @@ int fst_reader_create(const fst_reader_config_t *cfg, uint64_t *reader);
 int fst_reader_submit(uint64_t reader, const char *path, uint64_t file_offset, uint64_t nbytes,
                       uint64_t dst, uint64_t dst_len, uint64_t dst_offset, int64_t *request);
 
+/* Order every copy this reader issues from now on behind the work queued so far on `stream`
+ * (one event recorded there, waited for by all copy streams).  Call it after allocating a
+ * destination from a stream-ordered allocator and before fst_reader_submit: the memory may have
+ * belonged to a buffer that kernels already queued on `stream` still read, and the reader's copy
+ * streams are otherwise independent of it.  (Upstream needs no such call: its cudaMemcpy on the
+ * legacy default stream is ordered behind everything, ext.cpp:700-712.)  No-op for host readers. */
+int fst_reader_order_after(uint64_t reader, uint64_t stream);
+
 /* Block until the request's bytes are in the destination (DMA and kernels complete) or
  * timeout_ms passes (< 0: no limit).  *bytes_done receives the bytes delivered.  A failed or
- * short read returns FST_EIO after every window of the request has been drained.
+ * short read returns FST_EIO after every window of the request has been drained.  After
+ * FST_ETIMEOUT the request is still known: wait for it again with the same id.
  * Replaces nogds_file_reader::wait_read (ext.cpp:765-776) / gds_file_reader::wait_read. */
 int fst_reader_wait(uint64_t reader, int64_t request, int64_t timeout_ms, uint64_t *bytes_done);
 
@@ -231,7 +252,9 @@ int fst_gather(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_base, uint6
  *     can read a half-rewritten table.  Calls on one stream are ordered and safe.
  *   - The table is uploaded with cudaMemcpyAsync from ordinary (pageable) host memory, which
  *     returns once the runtime has staged the bytes, so the caller's ops array may be reused
- *     as soon as the call returns.
+ *     as soon as the call returns.  For such a copy the runtime first waits, on the host, for
+ *     the work already queued on `stream`: the calling thread stalls for that long, and other
+ *     threads calling fst_gather_static wait behind it (fst_gather callers do not).
  * Arguments, checks and results are those of fst_gather. */
 #define FST_GATHER_STATIC_MAX_OPS 4096
 int fst_gather_static(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_base,

@@ -8,9 +8,13 @@
 # source becomes part of this repository's history.  The result is test infrastructure only
 # (parity checker, and the CPU arm of bench.py); the product never imports it.
 #
-# usage: oracle/build_ref.sh [path-to-upstream-tree]
+# usage: oracle/build_ref.sh <path-to-upstream-tree>     (or FST_UPSTREAM_TREE in the environment)
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${FST_UPSTREAM_TREE:-}}"
+if [ -z "$REF" ]; then
+    echo "build_ref: no upstream tree given (argument or FST_UPSTREAM_TREE); keeping any prebuilt oracle/_ref" >&2
+    exit 0
+fi
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 OUT="$HERE/_ref"
 PY="${PYTHON:-python}"

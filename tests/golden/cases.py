@@ -6,7 +6,7 @@ from typing import Dict, List, Tuple
 
 import numpy as np
 
-from fastsafetensors_b200 import synth
+from tests import synth
 
 
 def owners(paths: List[str], world: int) -> Dict[int, List[str]]:

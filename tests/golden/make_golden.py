@@ -6,7 +6,7 @@ Run it where the upstream tree is available (it imports the build made by
     bash oracle/build_ref.sh && python tests/golden/make_golden.py
 
 Inputs are the tiny twins of the benchmark checkpoints, written deterministically by
-``fastsafetensors_b200.synth`` (so the tests can regenerate identical files), plus one crafted
+``tests.synth`` (so the tests can regenerate identical files), plus one crafted
 file with mixed dtypes.  Outputs are, per case, the shape, dtype and a 64-bit SHA-256 prefix of
 the bytes of every tensor each rank receives from upstream's ``get_tensor`` / ``get_sharded`` /
 ``get_multi_cols`` / ``push_tensor`` (CPU device, gloo ranks), and upstream's

@@ -6,7 +6,7 @@ uniform, as the configuration states) from which every tensor takes a window at 
 offset, so files are written at memory-copy speed, every tensor has distinct content, and any
 process can regenerate the exact bytes of any tensor from (seed, tensor index).
 
-``python -m fastsafetensors_b200.synth <config> <out_dir> [--scale tiny]`` writes a checkpoint.
+``python -m tests.synth <config> <out_dir> [--scale tiny]`` (from the repository root) writes a checkpoint.
 """
 
 from __future__ import annotations

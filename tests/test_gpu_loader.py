@@ -259,11 +259,15 @@ def test_loader_narrowing_on_cuda_matches_torch(tmp_path, leak_check):
 
 
 # ------------------------------------------------------------------ cuFile window source
-# Opt-in (FST_TEST_CUFILE=1): on machines without the nvidia-fs module libcufile can only run in
-# its compatibility mode, and on this pool's boxes (no nvidia-fs, no /run/udev) a call into it did
-# not return.
-needs_cufile = pytest.mark.skipif(os.environ.get("FST_TEST_CUFILE") != "1",
-                                  reason="cuFile tests are opt-in: set FST_TEST_CUFILE=1")
+# NVIDIA's libcufile itself: only where GPUDirect Storage proper can work (the nvidia-fs module is
+# loaded) AND the run asks for it.  Elsewhere the library refuses cuFile before opening its driver
+# (tests/test_gpu_cufile.py checks that, and runs the code path through a host-side double).
+def _real_cufile_allowed() -> bool:
+    return os.environ.get("FST_TEST_CUFILE") == "1" and bool(cpp.is_gds_supported(0))
+
+
+needs_cufile = pytest.mark.skipif(not _real_cufile_allowed(),
+                                  reason="needs the nvidia-fs module and FST_TEST_CUFILE=1")
 
 
 @needs_cufile
@@ -313,3 +317,80 @@ def test_loader_with_cufile_matches_upstream(golden, case_files, leak_check):
     assert got == golden["cases"][case["id"]][0]
     fb.close()
     loader.close()
+
+
+# ------------------------------------------------------------------ stream order of image reuse
+def test_reader_waits_for_pending_readers_of_reused_memory(tmp_path, leak_check):
+    """An image freed while a gather that reads it is still queued goes back to torch's allocator
+    and is handed to the next file image at once.  The reader fills that image from its own copy
+    streams, so it has to queue behind the caller's stream first (fst_reader_order_after);
+    otherwise its DMA overwrites bytes the pending gather has yet to read."""
+    from tests import synth
+
+    n = 192 << 20
+    specs = []
+    for k, seed in enumerate((21, 22)):
+        spec = synth.CheckpointSpec(f"reuse{k}", [synth.TensorSpec(f"w{k}", "U8", (n,), ("replicate",))], 1, seed)
+        specs.append((spec, synth.write_checkpoint(spec, str(tmp_path / f"c{k}"), fsync=False)[0]))
+    want = [synth.expected_bytes(s, 0) for s, _ in specs]
+    assert not np.array_equal(want[0], want[1])
+    torch.cuda.empty_cache()
+    loader = fst.SafeTensorsFileLoader(fst.SingleGroup(), DEV, nogds=True, max_threads=8)
+    loader.add_filenames({0: [specs[0][1]]})
+    fb = loader.copy_files_to_device()
+    t = fb.get_tensor("w0")
+    first_ptr = t.data_ptr()
+    out = torch.empty(n, dtype=torch.uint8, device=DEV)
+    # keep the stream busy for a while (large matmuls), then the gather that reads image 0
+    a = torch.randn(8192, 8192, device=DEV, dtype=torch.bfloat16)
+    for _ in range(150):
+        a = (a @ a).clamp_(-1, 1)
+    nat.gather([(t.data_ptr(), out.data_ptr(), 1, n, 0, 0)], int(torch.cuda.current_stream().cuda_stream),
+               (t.data_ptr(), n), (out.data_ptr(), n))
+    del t
+    fb.close()                        # image 0 goes back to the allocator with the gather pending
+    loader.reset()
+    loader.add_filenames({0: [specs[1][1]]})
+    fb = loader.copy_files_to_device()    # same size: the allocator hands out the same block
+    t1 = fb.get_tensor("w1")
+    reused = t1.data_ptr() == first_ptr
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), want[0]), "the pending gather read bytes of the next file"
+    assert np.array_equal(t1.cpu().numpy(), want[1])
+    del t1
+    fb.close()
+    loader.close()
+    assert reused, "the allocator did not reuse the block: the test did not exercise the hazard"
+
+
+def test_legacy_device_helpers():
+    """gpu_malloc / gpu_free / memcpy_h2d_async of upstream's module API."""
+    addr = cpp.gpu_malloc(1 << 20)
+    assert addr
+    host = cpp.cpu_malloc(1 << 20)
+    src = (np.arange(1 << 20) % 251).astype(np.uint8)
+    import ctypes
+
+    ctypes.memmove(host, src.ctypes.data, src.size)
+    assert cpp.memcpy_h2d_async(addr, host, src.size) == 0
+    torch.cuda.synchronize()
+
+    class _Span:
+        __cuda_array_interface__ = {"shape": (src.size,), "typestr": "|u1", "data": (addr, False), "version": 2}
+
+    got = torch.as_tensor(_Span(), device=DEV).cpu().numpy()
+    assert np.array_equal(got, src)
+    cpp.gpu_free(addr)
+    cpp.cpu_free(host)
+
+
+def test_gather_refuses_wrapping_address_arithmetic():
+    src = torch.zeros(4096, dtype=torch.uint8, device=DEV)
+    dst = torch.zeros(4096, dtype=torch.uint8, device=DEV)
+    s, d = src.data_ptr(), dst.data_ptr()
+    huge = (1 << 64) - 4096
+    for op in ((s, d, 3, 16, huge, 16), (s, d, 2, 16, 16, huge), (s, d, (1 << 63), 16, 16, 16)):
+        for entry in (nat.gather, nat.gather_static):
+            with pytest.raises(nat.NativeError) as e:
+                entry([op], 0, (s, 4096), (d, 4096))
+            assert e.value.code == nat.ERANGE, op

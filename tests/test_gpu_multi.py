@@ -50,3 +50,19 @@ def test_every_key_access_over_nccl(case_files, tmp_path):
             want[n] = digest_bytes(fo.raw(n))
     for rank in range(2):
         assert json.load(open(tmp_path / f"rank{rank}.json")) == want
+
+
+@pytest.mark.parametrize("queue_size", [0, 2])
+def test_pipeline_over_nccl_every_rank_gets_every_tensor(queue_size, case_files, tmp_path):
+    """ParallelLoader on two GPUs: batches of two files, each image broadcast once, producer and
+    consumer on different threads; every rank ends up with every tensor of every file."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from tests.test_parallel_loader import CASE, _expected
+    from tests.test_parallel_loader import _rank_main as pipeline_rank
+
+    paths = sorted(case_files(CASE))[:7]          # odd count: the last batch has one file only
+    want = {k: list(v) for k, v in _expected(paths).items()}
+    mp.spawn(pipeline_rank, args=(2, paths, free_port(), str(tmp_path), queue_size, "nccl"), nprocs=2, join=True)
+    for rank in range(2):
+        assert json.load(open(tmp_path / f"rank{rank}.json")) == want, rank

@@ -102,7 +102,7 @@ PACKED = [
 def _write_packed(path):
     import numpy as np
 
-    from fastsafetensors_b200 import synth
+    from tests import synth
     from oracle import st_oracle
 
     rng = np.random.default_rng(77)

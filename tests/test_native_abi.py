@@ -216,3 +216,44 @@ def test_legacy_nogds_reader_interface(blob_file, leak_check):
         reader.submit_read(0, buf, 0, 1 << 20, (4 << 20) - 10)
     cpp.cpu_free(addr)
     del reader
+
+
+def test_legacy_device_helpers_without_a_device():
+    """gpu_malloc / gpu_free / memcpy_h2d_async of upstream's module API (cpp.pyi:62-63,
+    ext.cpp:959-971): without a CUDA device they report failure the way upstream's do."""
+    if nat.cuda_device_count() > 0:
+        pytest.skip("a CUDA device is present")
+    assert cpp.gpu_malloc(4096) == 0
+    cpp.gpu_free(0)
+    host = cpp.cpu_malloc(4096)
+    assert cpp.memcpy_h2d_async(4096, host, 16) == -1
+    cpp.cpu_free(host)
+
+
+def test_wait_can_be_repeated_after_a_timeout(tmp_path):
+    """A wait that runs out of time leaves the request registered: the same id can be waited
+    for again and still reports the request's own outcome."""
+    data = np.random.default_rng(5).integers(0, 256, 6 << 20, dtype=np.uint8)
+    p = tmp_path / "blob.bin"
+    p.write_bytes(data.tobytes())
+    dst = np.zeros(data.size, dtype=np.uint8)
+    buf = cpp.gds_device_buffer(dst.ctypes.data, dst.size, False)
+    reader = cpp.Reader(-1, 1, 4096, 2, io_mode=nat.IO_DIRECT)   # 1536 small windows, one worker
+    try:
+        rid = reader.submit(str(p), 0, data.size, buf, 0)
+        timed_out = 0
+        for _ in range(200000):
+            try:
+                done = reader.wait(rid, 0)
+                break
+            except nat.NativeError as e:
+                assert e.code == nat.ETIMEOUT
+                timed_out += 1
+        else:
+            pytest.fail("the request never completed")
+        assert done == data.size and np.array_equal(dst, data)
+        with pytest.raises(nat.NativeError) as e:      # only now is the id forgotten
+            reader.wait(rid, 0)
+        assert e.value.code == nat.EINVAL
+    finally:
+        reader.close()

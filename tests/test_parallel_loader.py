@@ -81,12 +81,19 @@ def test_only_one_producer_is_supported(case_files):
         fst.ParallelLoader(None, case_files(CASE), max_concurrent_producers=2, device="cpu", nogds=True)
 
 
-def _rank_main(rank, world, paths, port, out_dir, queue_size):
+def _rank_main(rank, world, paths, port, out_dir, queue_size, backend="gloo"):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    device = "cpu"
+    if backend == "nccl":
+        torch.cuda.set_device(rank)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        device = f"cuda:{rank}"
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(device))
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
     it = fst.ParallelLoader(dist.group.WORLD, paths, queue_size=queue_size, use_tqdm_on_load=False,
-                            device="cpu", nogds=True, max_threads=2, slot_kb=64)
+                            device=device, nogds=True, max_threads=2, slot_kb=64)
     got = {}
     for key, t in it.iterate_weights():
         got[key] = (list(t.shape), digest_tensor(t))

@@ -4,8 +4,10 @@ Some processes cannot call the CUDA allocator when the loader runs: an inference
 already given all free HBM to its KV-cache pool (a cudaMalloc would fail), or one that bans
 cudaMalloc/cudaFree after start-up because both stall every stream of the device.  For them the
 library offers the same gather with its op table in a fixed device array that ships inside the
-library image.  This test drives it through the C ABI and requires byte-identical output to the
-ordinary entry point, twice in a row (the array is shared and keeps the previous call's table).
+library image.  This test drives it through the C ABI, twice in a row (the array is shared and
+keeps the previous call's table), and requires its output to be byte-identical both to a plain
+numpy restatement of the copies (canary bytes around them included) and to the ordinary entry
+point's.
 
 The file name sorts last on purpose: a run that stops at the first failure has then already run
 every other test.
@@ -35,6 +37,16 @@ def _random_ops(rng, n_ops, max_row_bytes):
     return ops, s_cur + 64, d_cur + 64
 
 
+def _expected(ops_rel, src_np, dst_size):
+    """What the copies must leave behind, computed on the host: row r of an op goes from
+    src[s + r * sp ..+rb) to dst[d + r * dp ..+rb); every other byte keeps the 0xA5 fill."""
+    want = np.full(dst_size, 0xA5, dtype=np.uint8)
+    for (s, d, rows, rb, sp, dp) in ops_rel:
+        for r in range(rows):
+            want[d + r * dp: d + r * dp + rb] = src_np[s + r * sp: s + r * sp + rb]
+    return want
+
+
 def _run(entry, ops_rel, src, dst_size):
     dst = torch.full((dst_size,), 0xA5, dtype=torch.uint8, device=DEV)
     ops = [(src.data_ptr() + o[0], dst.data_ptr() + o[1]) + tuple(o[2:]) for o in ops_rel]
@@ -50,10 +62,12 @@ def test_static_table_gather_matches_the_allocating_entry_point_twice():
     # from the first call sit behind the ones in use
     for n_ops, max_row in ((3000, 1500), (70, 9000)):
         ops_rel, s_size, d_size = _random_ops(rng, n_ops, max_row)
-        src = torch.from_numpy(rng.integers(0, 256, s_size, dtype=np.uint8)).to(DEV)
-        want = _run(nat.gather, ops_rel, src, d_size)
+        src_np = rng.integers(0, 256, s_size, dtype=np.uint8)
+        src = torch.from_numpy(src_np).to(DEV)
+        want = _expected(ops_rel, src_np, d_size)
         got = _run(nat.gather_static, ops_rel, src, d_size)
         assert np.array_equal(got, want), n_ops            # bit-exact, canaries included
+        assert np.array_equal(_run(nat.gather, ops_rel, src, d_size), want), n_ops
         assert (want != 0xA5).any()
 
 

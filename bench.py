@@ -1,32 +1,46 @@
-"""Benchmark of the safetensors -> HBM load path.
+"""Benchmark of the safetensors -> HBM tensor-parallel load path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--config NAME]
 
-Workload: the Llama-3-8B-shaped bf16 checkpoint (4 files, 16.06 GB of tensor data, synthetic
-values), loaded tensor-parallel.  With one GPU the single rank owns every file and packs the
-shards of all 8 tensor-parallel ranks (what the owner of a file does before the exchange); with N
-GPUs the files are owned round-robin, tensor parallelism is N-way and the shards are exchanged
-over NCCL.  One JSON line is printed by rank 0:
+Workload (synthetic values, the shapes of the benchmark configurations):
 
-* ``value``    GB/s of tensor data sharded per second with the file images already resident in
-               HBM (gather kernel + exchange), timed with CUDA events, max over ranks;
+* N = 1: the Llama-2-13B-shaped checkpoint (3 files, 26.03 GB, fp16 weights and fp32 norms, odd
+  header lengths so that every window goes through the realign kernel): the largest
+  configuration that fits one GPU.  The single rank owns every file and packs the shards of all
+  4 tensor-parallel ranks (what the owner of a file does before the exchange).
+* N > 1: the first 8 of the 30 files of the Llama-3-70B-shaped checkpoint (37.6 GB of 141 GB:
+  what fits the boxes' disk), owned round-robin, tensor parallelism N-way, shards exchanged over
+  NVLink.  ``--config`` / ``--files`` select any other configuration.
+
+One JSON line is printed by rank 0:
+
+* ``value``    GB/s of tensor data turned into shards per second with the file images already
+               resident in memory (gather kernel + exchange), CUDA events, max over ranks;
 * ``e2e``      the same checkpoint from files on disk to shards in HBM through the public loader
                API, page cache dropped before every step (cold reads), wall clock between device
-               synchronisations; ``e2e_warm`` is the same with the files in the page cache;
+               synchronisations, max over ranks; ``e2e_warm``: files in the page cache;
+* ``storage_read`` cold O_DIRECT read rate of the same files with the loader's own request
+               pattern, measured before, between and after the cold steps;
 * ``roofline`` the gather kernel against the measured HBM copy bandwidth;
-* ``cpu_baseline`` upstream fastsafetensors (CPU, gloo ranks) on a bounded sample.
+* ``parity``   a sample of the shards compared byte for byte with regenerated tensor data;
+* ``reference_cuda`` upstream's own CUDA path (``device=cuda:r``, NCCL) on the same files at this N;
+* ``cpu_baseline`` upstream fastsafetensors (CPU, gloo ranks) on a bounded sample (N = 1 only).
 
-``--impl reference`` runs upstream's own CPU path (built into ``oracle/_ref``) on the same files.
+``--impl reference`` runs upstream's own CPU path (built into ``oracle/_ref``) on the same files
+and reports the same two quantities: ``value`` = file images resident in host memory -> shards
+(upstream's shuffle phase), ``e2e`` = cold files -> shards.
 """
 
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import statistics
 import subprocess
 import sys
+import threading
 import time
 from collections import OrderedDict
 
@@ -35,8 +49,11 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 GB = 1e9
-WORKLOAD = "llama3-8b"
 L2_BYTES = 126 * (1 << 20)
+METRIC = ("safetensors->HBM tensor-parallel load: GB/s of tensor data sharded with file images "
+          "resident (value), files on disk -> shards (e2e)")
+# bytes of cold reading an arm spends on timed end-to-end steps (bounds the step count)
+E2E_COLD_BYTES = 200e9
 
 
 def parse_args():
@@ -44,24 +61,31 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=("b200", "reference", "reference-cuda"))
-    ap.add_argument("--config", default=WORKLOAD)
+    ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    ap.add_argument("--config", default=None,
+                    help="gpt2-small | llama3-8b | llama2-13b | llama3-70b | mixtral-8x7b "
+                         "(default: llama2-13b on one GPU, llama3-70b otherwise)")
+    ap.add_argument("--files", type=int, default=0,
+                    help="keep only the first F files of the checkpoint (default: all, 8 for llama3-70b)")
     ap.add_argument("--scale", default="full", choices=("full", "tiny"))
     ap.add_argument("--dir", default=os.environ.get("FST_BENCH_DIR", "/tmp/fst_bench"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-reference-cuda", action="store_true")
     ap.add_argument("--warm-only", action="store_true", help="skip the cold end-to-end phase and the storage roofline")
-    ap.add_argument("--threads", type=int, default=int(os.environ.get("FST_BENCH_THREADS", 16)),
-                    help="reader threads (max_threads of the loader)")
+    ap.add_argument("--e2e-steps", type=int, default=0, help="cold end-to-end steps (default: by checkpoint size)")
+    ap.add_argument("--threads", type=int, default=int(os.environ.get("FST_BENCH_THREADS", 0)),
+                    help="reader threads per rank (default: host CPUs / ranks, between 2 and 16)")
     ap.add_argument("--transport", default=os.environ.get("FST_B200_TRANSPORT", "auto"),
                     choices=("auto", "nccl", "peer"),
                     help="N > 1: all_to_all over NCCL, gather-kernel stores into peer arenas, or the "
-                         "library's own choice (peer for two ranks, else NCCL)")
+                         "library's own choice")
     ap.add_argument("--ref-settings", default="best", choices=("best", "defaults", "tuned"),
                     help="--impl reference: upstream's library defaults, the rule of its perf tool, or "
                          "whichever of the two is faster in one untimed step each")
-    ap.add_argument("--ref-budget", type=float, default=150.0,
-                    help="--impl reference: seconds the cold phase may take before it is cut to fewer files")
+    ap.add_argument("--ref-budget", type=float, default=240.0,
+                    help="--impl reference: seconds the resident phase may take before its steps are cut "
+                         "to the first files of the checkpoint")
     ap.add_argument("--layers", type=int, default=0,
                     help="keep only the first L transformer layers (small case for profiler captures)")
     ap.add_argument("--other-kernels-only", action="store_true",
@@ -126,7 +150,7 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------
-# workload
+# workload (shared by both arms; nothing here touches the loader under test)
 # ------------------------------------------------------------------------------------------
 def plan_for(spec, tp: int) -> "OrderedDict[str, tuple]":
     return OrderedDict((t.name, (t.action[0], t.action[1] % tp) if t.action[0] == "push" else t.action)
@@ -141,34 +165,134 @@ def read_into_page_cache(paths) -> None:
                 pass
 
 
-def load_spec(args):
-    """The checkpoint spec of the run; ``--layers L`` cuts it to the first L layers."""
-    import re
+class Workload:
+    """Files, tensors and plan of one run.  ``--layers L`` cuts the checkpoint to its first L
+    layers, ``--files F`` to the tensors of its first F files (file boundaries stay those of the
+    whole checkpoint)."""
+
+    def __init__(self, args, world: int):
+        import re
+
+        from tests import synth
+
+        name = args.config or ("llama2-13b" if world == 1 else "llama3-70b")
+        spec = synth.config(name, args.scale)
+        if args.layers > 0:
+            def keep(tname: str) -> bool:
+                m = re.search(r"(?:layers|h)\.(\d+)\.", tname)
+                return m is None or int(m.group(1)) < args.layers
+            spec.tensors = [t for t in spec.tensors if keep(t.name)]
+            spec.name = f"{spec.name}-first{args.layers}layers"
+        self.spec = spec
+        self.groups = synth.partition(spec)
+        self.total_files = len(self.groups)
+        n_files = args.files or (8 if name == "llama3-70b" and args.scale == "full" else self.total_files)
+        self.n_files = max(1, min(n_files, self.total_files))
+        self.tp = spec.tp if world == 1 else world
+        self.indices = [i for g in self.groups[: self.n_files] for i in g]   # tensor indices in the kept files
+        self.tensors = [spec.tensors[i] for i in self.indices]
+        self.data_bytes = sum(t.nbytes for t in self.tensors)
+        full = plan_for(spec, self.tp)
+        self.plan = OrderedDict((t.name, full[t.name]) for t in self.tensors)
+        self.dir = os.path.join(args.dir, spec.name)
+        self.paths = sorted(os.path.join(self.dir, synth.file_name(spec, k, self.total_files))
+                            for k in range(self.n_files))
+        subset = "" if self.n_files == self.total_files else \
+            f" (first {self.n_files} of its {self.total_files} files)"
+        self.label = (f"{spec.name} ({args.scale}){subset}: {len(self.tensors)} tensors, "
+                      f"{self.n_files} files, {self.data_bytes} data bytes, tensor-parallel {self.tp}-way")
+
+    def config_block(self) -> dict:
+        """The ``config`` object: identical in both arms."""
+        return {"workload": self.label, "tp": self.tp, "files": self.n_files, "data_bytes": self.data_bytes,
+                "l2": f"every step moves far more than L2 ({L2_BYTES} B); no flush between steps"}
+
+    def write(self, rank: int, barrier) -> None:
+        from tests import synth
+
+        if rank == 0:
+            t0 = time.time()
+            synth.write_checkpoint(self.spec, self.dir, fsync=True, only_files=range(self.n_files))
+            sys.stderr.write(f"[bench] checkpoint {self.label} in {self.dir} ({time.time() - t0:.1f} s)\n")
+        barrier()
+
+    def e2e_steps(self, args) -> int:
+        if args.e2e_steps > 0:
+            return args.e2e_steps
+        return int(max(2, min(args.steps, round(E2E_COLD_BYTES / max(self.data_bytes, 1)))))
+
+
+def host_threads(args, world: int) -> int:
+    if args.threads > 0:
+        return args.threads
+    return int(max(2, min(16, (os.cpu_count() or 16) // max(1, world))))
+
+
+# ------------------------------------------------------------------------------------------
+# parity inside the bench: a sample of the produced shards against regenerated tensor bytes
+# ------------------------------------------------------------------------------------------
+def expected_shard(tensor, raw, action, dst: int, tp: int):
+    """Bytes rank ``dst`` must hold for ``tensor`` (numpy): block ``dst`` of ceil(n/tp) on the
+    split dimension, the whole tensor for replicated and pushed ones."""
+    import numpy as np
 
     from tests import synth
 
-    spec = synth.config(args.config, args.scale)
-    if args.layers > 0:
-        def keep(name: str) -> bool:
-            m = re.search(r"(?:layers|h)\.(\d+)\.", name)
-            return m is None or int(m.group(1)) < args.layers
-        spec.tensors = [t for t in spec.tensors if keep(t.name)]
-        spec.name = f"{spec.name}-first{args.layers}layers"
-    return spec
+    if action[0] != "shard":
+        return raw
+    item = synth._ITEMSIZE[tensor.dtype]
+    dim = action[1]
+    a = raw.reshape(*tensor.shape, item)
+    block = -(-tensor.shape[dim] // tp)
+    sl = [slice(None)] * len(tensor.shape)
+    sl[dim] = slice(dst * block, (dst + 1) * block)
+    return np.ascontiguousarray(a[tuple(sl)]).reshape(-1)
 
 
-def prepare_files(spec, directory: str, rank: int, barrier) -> list:
+def parity_sample(wl: Workload, want: int = 40, max_bytes: int = 600 << 20):
+    """Deterministic sample of positions in ``wl.tensors``: the first tensor of every kind of
+    action (dim 0, dim 1, replicated, pushed) and an even stride over the rest."""
+    first, rest = {}, []
+    for pos, t in enumerate(wl.tensors):
+        if t.nbytes > max_bytes:
+            continue
+        kind = wl.plan[t.name][:2] if wl.plan[t.name][0] == "shard" else wl.plan[t.name][:1]
+        if kind not in first:
+            first[kind] = pos
+        else:
+            rest.append(pos)
+    stride = max(1, len(rest) // max(1, want - len(first)))
+    return sorted(set(first.values()) | set(rest[::stride][: want]))
+
+
+def check_parity(wl: Workload, get_result, dsts) -> dict:
+    """``get_result(name, dst)`` -> torch tensor (or None where ``dst`` does not get the tensor).
+    Compares SHA-256 of the produced bytes with the regenerated ones for every ``dst`` in ``dsts``."""
+    import torch
+
     from tests import synth
 
-    out = os.path.join(directory, f"{spec.name}")
-    if rank == 0:
-        t0 = time.time()
-        paths = synth.write_checkpoint(spec, out, fsync=True)
-        sys.stderr.write(f"[bench] checkpoint {spec.name}: {len(paths)} files, "
-                         f"{spec.data_bytes / GB:.2f} GB in {out} ({time.time() - t0:.1f} s)\n")
-    barrier()
-    groups = synth.partition(spec)
-    return sorted(os.path.join(out, synth.file_name(spec, k, len(groups))) for k in range(len(groups)))
+    checked, bad, kinds = 0, [], set()
+    for pos in parity_sample(wl):
+        t = wl.tensors[pos]
+        action = wl.plan[t.name]
+        raw = synth.expected_bytes(wl.spec, wl.indices[pos])
+        for dst in dsts:
+            got = get_result(t.name, dst)
+            if action[0] == "push" and action[1] != dst:
+                if got is not None:
+                    bad.append(f"{t.name}@{dst}: present on a rank it was not pushed to")
+                continue
+            if got is None:
+                bad.append(f"{t.name}@{dst}: missing")
+                continue
+            have = got.contiguous().reshape(-1).view(torch.uint8).cpu().numpy()
+            exp = expected_shard(t, raw, action, dst, wl.tp)
+            if hashlib.sha256(have.tobytes()).digest() != hashlib.sha256(exp.tobytes()).digest():
+                bad.append(f"{t.name}@{dst}: bytes differ")
+            checked += 1
+            kinds.add(action[0] + (str(action[1]) if action[0] == "shard" else ""))
+    return {"checked": checked, "ok": not bad, "kinds": sorted(kinds), "mismatches": bad[:5]}
 
 
 # ------------------------------------------------------------------------------------------
@@ -179,11 +303,10 @@ def b200_arm(args) -> dict:
     import torch.distributed as dist
 
     import fastsafetensors_b200 as fst
-    from fastsafetensors_b200 import _native as nat
     from fastsafetensors_b200 import cpp
-    from tests import synth
     from fastsafetensors_b200.batch import PeerArenaUnavailable, PeerShardExchange, ShardExchange
     from fastsafetensors_b200.file_buffer import resolve_transport
+    from tests import synth
 
     rank, local_rank, world = dist_env()
     if not torch.cuda.is_available():
@@ -194,8 +317,11 @@ def b200_arm(args) -> dict:
     if world > 1:
         import datetime
 
+        # no all-reduce of any size is on the path; NVLS buys nothing here and a rank that leaves
+        # early while bound to a multicast object can disturb its peers
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device(device),
-                                timeout=datetime.timedelta(seconds=180))
+                                timeout=datetime.timedelta(seconds=900))
         pg = dist.group.WORLD
 
     def barrier():
@@ -209,30 +335,44 @@ def b200_arm(args) -> dict:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def all_ranks(obj) -> list:
+        if world == 1:
+            return [obj]
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
+    def note(msg: str) -> None:
+        if rank == 0:
+            sys.stderr.write(f"[bench] {time.strftime('%H:%M:%S')} {msg}\n")
+            sys.stderr.flush()
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
     if args.other_kernels_only:
-        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
         return {"other_kernels": other_kernels(device, peak)} if rank == 0 else {}
-    spec = load_spec(args)
-    tp = spec.tp if world == 1 else world
-    plan = plan_for(spec, tp)
-    paths = prepare_files(spec, args.dir, rank, barrier)
+
+    wl = Workload(args, world)
+    tp, plan, paths, data_bytes = wl.tp, wl.plan, wl.paths, wl.data_bytes
+    wl.write(rank, barrier)
     owners = synth.owners(paths, world)
-    data_bytes = spec.data_bytes
+    threads = host_threads(args, world)
 
     def open_loader():
         return fst.SafeTensorsFileLoader(pg if pg is not None else fst.SingleGroup(), torch.device(device),
-                                         nogds=True, max_threads=args.threads)
+                                         nogds=True, max_threads=threads)
 
-    # "auto" is the library's rule: the fused peer exchange where it measured faster (two ranks),
-    # the NCCL all-to-all otherwise, and NCCL on all ranks together if peer mapping is refused
+    # "auto" is the library's rule, and NCCL on all ranks together if peer mapping is refused
     may_fall_back = False
     if world > 1:
         want = resolve_transport(args.transport, world, fst.Device.from_str(device))
         may_fall_back = want == "auto"
         args.transport = "nccl" if want == "nccl" else "peer"
 
-    def make_exchange(fb) -> ShardExchange:
+    def make_exchange(fb):
         if world > 1 and args.transport == "peer":
             try:
                 return PeerShardExchange(fb, plan, tp, rank)
@@ -243,28 +383,25 @@ def b200_arm(args) -> dict:
                 args.transport = "nccl"
         return ShardExchange(fb, plan, tp, rank if world > 1 else 0, local=(world == 1))
 
-    def note(msg: str) -> None:
-        if rank == 0:
-            sys.stderr.write(f"[bench] {time.strftime('%H:%M:%S')} {msg}\n")
-            sys.stderr.flush()
-
     # ---------------------------------------------------------------- device-resident phase
+    note(f"{wl.label}; {threads} reader threads per rank")
     note("device-resident phase: loading images")
     loader = open_loader()
     loader.add_filenames(owners)
     fb = loader.copy_files_to_device()
     ex = make_exchange(fb)
     stream = torch.cuda.current_stream()
+    warmup = max(3, args.warmup)
     # clocks are sampled every 200 ms from here to the end of the timed region; the warm-up runs
     # for at least 1.5 s so that the short timed region is bracketed by samples taken under load
     sampler = ClockSampler(local_rank) if rank == 0 else None
     # every rank must run the same number of steps (each step ends in a collective when N > 1):
     # time the first warm-up steps, then agree on how many more fill the 1.5 s
     t_w = time.perf_counter()
-    for _ in range(max(3, args.warmup)):
+    for _ in range(warmup):
         ex.run()
     torch.cuda.synchronize()
-    per_step = (time.perf_counter() - t_w) / max(3, args.warmup)
+    per_step = (time.perf_counter() - t_w) / warmup
     extra = 0 if args.kernel_only else int(max_over_ranks(min(2000.0, 1.5 / max(per_step, 1e-6))))
     for i in range(extra):
         ex.run()
@@ -288,76 +425,91 @@ def b200_arm(args) -> dict:
     kernel_ms_total = sum(a.elapsed_time(b) for a, b in kernel_events)
     n_launch = len(kernel_events)
     launches_timed = m1.kernel_launches - m0.kernel_launches
-    payload_per_step = ex.payload_bytes                      # bytes this rank's kernel moves
+    payload_per_step = ex.payload_bytes                      # bytes this rank's kernel moves per step
+    # the roofline entry is the kernel over the timed launches: algorithmic bytes of a launch =
+    # 2 x its payload (read once, written once); per launch, the average over the launches of a step
+    launches_per_step = max(1, n_launch // max(1, args.steps))
+    alg_bytes_per_launch = 2.0 * payload_per_step / launches_per_step
     kernel_ms = kernel_ms_total / max(1, n_launch)           # average launch duration
-    alg_bytes_per_launch = 2.0 * payload_per_step * args.steps / max(1, n_launch)
     achieved = alg_bytes_per_launch / (kernel_ms * 1e-3) / GB if kernel_ms > 0 else 0.0
     clocks = sampler.stop() if sampler else None
-    egress = sum(ex.layout.region_bytes[rank][d] for d in range(tp) if d != rank) if world > 1 else 0
-    # a light checksum of the result so the step has a device->host read
+    egress = ex.egress_bytes if world > 1 else 0
+
+    # parity: a sample of what the timed steps produced, against regenerated tensor bytes
+    note("parity sample")
+    if world == 1:
+        per_dst = ex.results()
+        parity = check_parity(wl, lambda n, d: (per_dst[d][n].get_raw() if n in per_dst[d] else None), range(tp))
+        per_dst = None
+    else:
+        mine = ex.results()
+        parity = check_parity(wl, lambda n, d: (mine[n].get_raw() if n in mine else None), [rank])
+        mine = None
+        every = all_ranks(parity)
+        parity = {"checked": sum(p["checked"] for p in every), "ok": all(p["ok"] for p in every),
+                  "kinds": sorted(set(k for p in every for k in p["kinds"])),
+                  "mismatches": [m for p in every for m in p["mismatches"]][:5]}
+    parity["what"] = "SHA-256 of result bytes (device -> host) against regenerated tensor data, after the timed steps"
+    # a light device -> host read of the result
     check = int(ex.recv[:: max(1, ex.recv.numel() // 4096)].to(torch.int64).sum().item())
-    if isinstance(ex, PeerShardExchange):
-        ex.finish()
     del ex
     fb.close()
     loader.close()
     torch.cuda.empty_cache()
 
-    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(peaks_path):
-        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
-    else:
-        peak, peak_src = 6650.0, "fallback"
-
     result = {
-        "metric": "safetensors->HBM tensor-parallel load throughput",
+        "metric": METRIC,
         "value": round(data_bytes / (resident_ms * 1e-3) / GB, 2),
         "unit": "GB/s",
-        "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "n_gpus": world, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(resident_ms, 4),
         "higher_is_better": True,
         "scaling": "strong",
         "vs_baseline": None,
         "dtype": "u8",
         "data": "synthetic",
-        "config": {
-            "workload": f"{spec.name} ({args.scale}): {len(spec.tensors)} tensors, {len(paths)} files, "
-                        f"{data_bytes} data bytes, tensor-parallel {tp}-way"
-                        + (" packed by one rank for all destinations" if world == 1 else
-                           " files owned round-robin, " + ("NCCL all-to-all" if args.transport == "nccl"
-                                                            else "gather kernel stores into peer arenas (NVLink)")),
+        "config": wl.config_block(),
+        "notes": {
             "value_phase": "file images resident in HBM -> gather kernel (+ exchange)",
-            "l2": f"inputs ({payload_per_step} B per rank and step) larger than L2 ({L2_BYTES} B), no flush",
-            "tp": tp,
+            "how": ("one rank packs the shards of all destinations" if world == 1 else
+                    "files owned round-robin, " + ("chunked NCCL all-to-all overlapped with the gather launches"
+                                                   if args.transport == "nccl"
+                                                   else "gather kernel stores into peer arenas (NVLink)")),
+            "payload_bytes_per_rank_and_step": int(payload_per_step),
+            "reader_threads_per_rank": threads,
         },
         "gpu_launches": int(launches_timed),
         "roofline": {
             "bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
             "frac": round(achieved / peak, 4),
-            # dram read+write bytes of one launch: the ncu capture of a small case of this kernel
-            # gave 0.993 x its algorithmic bytes (no re-reads); traffic grows in proportion
-            "traffic": int(0.993 * alg_bytes_per_launch) if world == 1 else None,
-            "traffic_source": "ncu small case x units processed (profiles/fst_gather_kernel_llama3-8b.md)"
-                              if world == 1 else None,
             "peak_source": peak_src,
             "kernel": "fst_gather_kernel", "launches": n_launch,
             "avg_launch_ms": round(kernel_ms, 4),
             "algorithmic_bytes_per_launch": int(alg_bytes_per_launch),
         },
         "clocks": clocks,
+        "parity": parity,
         "result_checksum": check,
     }
+    result["roofline"].update(recorded_traffic(alg_bytes_per_launch))
     if world > 1:
+        peer_ref = measure_peer_copy(barrier, max_over_ranks) if not args.kernel_only else None
+        egress_max = max(all_ranks(egress))
+        rate = egress_max / (resident_ms * 1e-3) / GB
         # every byte a rank sends crosses NVLink once; with the step time this is the per-GPU
-        # egress rate the exchange sustains (measured peer-copy reference: 770 GB/s per direction)
-        result["nvlink"] = {"transport": args.transport, "egress_bytes_per_rank_and_step": int(egress),
-                            "egress_gbs_per_gpu": round(egress / (resident_ms * 1e-3) / GB, 1),
-                            "reference_peer_copy_gbs": 770.0,
-                            "note": "step time includes the gather kernel and the exchange"}
+        # egress rate the exchange sustains
+        result["nvlink"] = {"transport": args.transport, "egress_bytes_per_rank_and_step": int(egress_max),
+                            "egress_gbs_per_gpu": round(rate, 1),
+                            "peer_copy_gbs_measured": peer_ref,
+                            "frac_of_peer_copy": round(rate / peer_ref, 3) if peer_ref else None,
+                            "note": "egress of the rank that sends most over the whole step (gather "
+                                    "launches + exchange); the reference is one 1 GiB device-to-device "
+                                    "copy to the neighbouring GPU, all ranks at once, slowest rank"}
         if args.transport == "peer":
             # fused pack + transfer: the step cannot be faster than the slower of moving this
             # rank's payload through HBM and pushing its remote part through NVLink
-            target_ms = max(2.0 * payload_per_step / (peak * GB), egress / (770.0 * GB)) * 1e3
+            link = peer_ref or 770.0
+            target_ms = max(2.0 * payload_per_step / (peak * GB), egress / (link * GB)) * 1e3
             result["nvlink"]["fused_kernel"] = {"target_ms": round(target_ms, 4),
                                                 "achieved_ms": round(kernel_ms, 4),
                                                 "frac": round(target_ms / kernel_ms, 4) if kernel_ms else None}
@@ -370,84 +522,187 @@ def b200_arm(args) -> dict:
         ld = open_loader()
         ld.add_filenames(owners)
         t1 = time.perf_counter()
-        buf = ld.copy_files_to_device()
-        t2 = time.perf_counter()
+        buf = ld.copy_files_to_device(wait=False)     # reads queued; files are waited for in order
         if world == 1:
             got = buf.shard_locally(plan, tp)
             probe = next(iter(got[-1].values())).get_raw()
         else:
             got = buf.exchange(plan, transport=args.transport)
             probe = next(iter(got.values())).get_raw()
+        t2 = time.perf_counter()
         head = probe.reshape(-1)[:1024].cpu()      # device -> host read of the result
         torch.cuda.synchronize()
-        barrier()
         t3 = time.perf_counter()
+        barrier()
+        t4 = time.perf_counter()
         del got, probe
         buf.close()
         ld.close()
-        return max_over_ranks(t3 - t0), int(head.numel() * head.element_size()), (t1 - t0, t2 - t1, t3 - t2)
+        return (max_over_ranks(t4 - t0), int(head.numel() * head.element_size()),
+                {"open_and_headers": t1 - t0, "read_pack_exchange_queued": t2 - t1, "device_drain": t3 - t2,
+                 "wait_for_other_ranks": t4 - t3, "total": t4 - t0})
 
-    def e2e_phase(cold: bool, steps: int, warmup: int):
-        times, d2h, parts = [], 0, []
+    def cold_read_pass() -> float:
+        """One pass of the storage roofline: every rank reads the files it owns, all submitted at
+        once (the loader's pattern), O_DIRECT, into host memory; GB/s over all ranks."""
+        if rank == 0:
+            synth.drop_page_cache(paths)
+        barrier()
+        dt = max_over_ranks(read_files_direct(owners[rank], threads))
+        return sum(os.path.getsize(p) for p in paths) / dt / GB
+
+    def e2e_phase(cold: bool, steps: int, warmup_steps: int, passes_at=()):
+        times, d2h, parts, passes = [], 0, [], []
         r0 = cpp.get_cpp_metrics().read_ns
-        for i in range(warmup + steps):
+        for i in range(warmup_steps + steps):
+            if i - warmup_steps in passes_at:
+                passes.append(round(cold_read_pass(), 3))
             if cold:
                 if rank == 0:
                     synth.drop_page_cache(paths)
                 barrier()
-            if i == warmup:
+            if i == warmup_steps:
                 r0 = cpp.get_cpp_metrics().read_ns
             dt, d2h, part = e2e_step()
-            if i >= warmup:
+            if i >= warmup_steps:
                 times.append(dt)
                 parts.append(part)
             torch.cuda.empty_cache()
+        if steps in passes_at:
+            passes.append(round(cold_read_pass(), 3))
         mean = sum(times) / len(times)
         read_s = (cpp.get_cpp_metrics().read_ns - r0) / 1e9 / len(times)
+        mine = {k: round(sum(p[k] for p in parts) / len(parts), 4) for k in parts[0]}
+        mine["pread_thread_seconds"] = round(read_s, 3)
+        mine["rank"] = rank
+        slowest = max(all_ranks(mine), key=lambda p: p["total"] - p["wait_for_other_ranks"])
         return {"value": round(data_bytes / mean / GB, 3), "unit": "GB/s",
                 "h2d_bytes_per_step": int(data_bytes), "d2h_bytes_per_step": d2h,
-                "s_per_step": round(mean, 4), "steps": steps, "warmup": warmup,
+                "s_per_step": round(mean, 4), "steps": steps, "warmup": warmup_steps,
+                "s_per_step_min_max": [round(min(times), 4), round(max(times), 4)],
                 "page_cache": "dropped before every step" if cold else "warm",
-                "rank0_phases_s": {"open_and_headers": round(sum(p[0] for p in parts) / len(parts), 4),
-                                   "copy_files_to_device": round(sum(p[1] for p in parts) / len(parts), 4),
-                                   "shard_and_sync": round(sum(p[2] for p in parts) / len(parts), 4),
-                                   "pread_thread_seconds": round(read_s, 3)}}
+                "slowest_rank_phases_s": slowest}, passes
 
     note(f"device-resident phase done: {resident_ms:.3f} ms per step")
-    if rank == 0:
+    if rank == 0 and not args.kernel_only:
         result["other_kernels"] = other_kernels(device, peak)
     if not args.no_e2e and not args.kernel_only:
-        note("end-to-end phase, cold")
-        mA = cpp.get_cpp_metrics()
+        cold_steps = wl.e2e_steps(args)
         if not args.warm_only:
-            result["e2e"] = e2e_phase(True, args.steps, min(3, max(1, args.warmup)))
+            note(f"end-to-end phase, cold ({cold_steps} steps, storage read passes before, between and after)")
+            mA = cpp.get_cpp_metrics()
+            result["e2e"], passes = e2e_phase(True, cold_steps, 1, passes_at=(0, cold_steps // 2, cold_steps))
             mB = cpp.get_cpp_metrics()
             result["e2e"]["io"] = {"direct_requests": mB.direct_io_requests - mA.direct_io_requests,
                                    "buffered_requests": mB.buffered_io_requests - mA.buffered_io_requests}
+            result["storage_read"] = {
+                "cold_direct_gbs_max": max(passes), "cold_direct_gbs_median": statistics.median(passes),
+                "passes_gbs": passes, "threads_per_rank": threads, "block": "4 MiB",
+                "reading_ranks": sum(1 for r in owners if owners[r]),
+                "tool": "native reader, O_DIRECT, all owned files submitted at once, host destination "
+                        "(fio is not installed); passes before, between and after the cold steps"}
+            result["e2e"]["frac_of_storage_read"] = round(result["e2e"]["value"] / max(passes), 3)
+            result["e2e"]["frac_of_storage_read_median"] = round(
+                result["e2e"]["value"] / statistics.median(passes), 3)
         note("end-to-end phase, warm")
         if rank == 0:
             read_into_page_cache(paths)
         barrier()
         mC = cpp.get_cpp_metrics()
-        result["e2e_warm"] = e2e_phase(False, min(args.steps, 3), 3)
+        result["e2e_warm"], _ = e2e_phase(False, min(args.steps, 3), 2)
         mD = cpp.get_cpp_metrics()
         result["e2e_warm"]["io"] = {"direct_requests": mD.direct_io_requests - mC.direct_io_requests,
                                     "buffered_requests": mD.buffered_io_requests - mC.buffered_io_requests}
-        if not args.warm_only:
-            note("storage read roofline")
-            result["storage_read"] = storage_roofline(paths, owners[rank], rank, barrier, max_over_ranks)
-        if not args.warm_only and result["storage_read"]["cold_direct_gbs"]:
-            result["e2e"]["frac_of_storage_read"] = round(
-                result["e2e"]["value"] / result["storage_read"]["cold_direct_gbs"], 3)
+    if not parity["ok"]:
+        note(f"PARITY FAILURE: {parity['mismatches']}")
+    # ---------------------------------------------------------------- upstream's CUDA path, same N
+    if not args.no_reference_cuda and not args.kernel_only and not args.no_e2e:
+        note("upstream's CUDA path on the same files")
+        result["reference_cuda"] = reference_cuda_phase(wl, owners, pg, rank, world, device, barrier,
+                                                        max_over_ranks, result if rank == 0 else None)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    if rank == 0 and not args.no_cpu_baseline and not args.kernel_only:
-        note("cpu baseline (upstream on the host cores)")
-        result["cpu_baseline"] = cpu_baseline(spec, paths, tp)
-        if world == 1:
-            result["reference_cuda_nogds"] = reference_cuda_subprocess(args)
-    return result if rank == 0 else {}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.kernel_only:
+        note("cpu baseline (upstream on the host cores, bounded sample)")
+        result["cpu_baseline"] = cpu_baseline(wl)
+    return result if rank == 0 else {"parity_ok": parity["ok"]}
+
+
+def recorded_traffic(alg_bytes_per_launch: float) -> dict:
+    """DRAM traffic of a gather launch from the recorded profiler capture: the ratio of dram
+    read+write bytes to algorithmic bytes measured on a small case of this kernel, kept in
+    ``profiles/fst_gather_kernel_traffic.json`` with a hash of the kernel source it was taken
+    from.  Traffic grows in proportion to the units processed, so the ratio scales to a full
+    launch.  If the source has changed since the capture the figure is marked as a constant."""
+    path = os.path.join(ROOT, "profiles", "fst_gather_kernel_traffic.json")
+    try:
+        rec = json.load(open(path))
+        src = os.path.join(ROOT, "fastsafetensors_b200", "csrc", "fst_kernels.cu")
+        current = hashlib.sha256(open(src, "rb").read()).hexdigest()[:16]
+        ratio = float(rec["dram_bytes_per_algorithmic_byte"])
+    except (OSError, ValueError, KeyError):
+        return {"traffic": None, "traffic_source": "no recorded capture"}
+    fresh = current == rec.get("kernel_source_sha256_16")
+    return {"traffic": int(ratio * alg_bytes_per_launch),
+            "traffic_source": ("profiler capture of a small case x units processed"
+                               if fresh else "constant: the kernel source changed after the recorded capture"),
+            "traffic_ratio": ratio}
+
+
+def measure_peer_copy(barrier, max_over_ranks):
+    """GB/s of one device-to-device copy of 1 GiB from this GPU to its neighbour (best of 5),
+    all ranks at once; the slowest rank's figure: the NVLink reference the exchange is held
+    against."""
+    import torch
+
+    n = 1 << 30
+    try:
+        me = torch.cuda.current_device()
+        src = torch.empty(n, dtype=torch.uint8, device=f"cuda:{me}")
+        dst = torch.empty(n, dtype=torch.uint8, device=f"cuda:{(me + 1) % torch.cuda.device_count()}")
+        best = 0.0
+        for i in range(7):
+            torch.cuda.synchronize()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            dst.copy_(src, non_blocking=True)
+            b.record()
+            torch.cuda.synchronize()
+            if i >= 2:
+                best = max(best, n / (a.elapsed_time(b) * 1e-3) / GB)
+        del src, dst
+        torch.cuda.empty_cache()
+        return round(-max_over_ranks(-best), 1)
+    except Exception as e:  # noqa: BLE001
+        sys.stderr.write(f"[bench] peer copy measurement failed: {e}\n")
+        max_over_ranks(0.0)
+        return None
+
+
+def read_files_direct(my_paths, threads: int) -> float:
+    """Seconds to read ``my_paths`` cold with the loader's reader settings (O_DIRECT, 4 MiB
+    windows, two slots per thread), every file submitted before the first wait, into one host
+    buffer that all requests share (the bytes are thrown away)."""
+    import numpy as np
+
+    from fastsafetensors_b200 import _native as nat
+    from fastsafetensors_b200 import cpp
+
+    if not my_paths:
+        return 0.0
+    sizes = [os.path.getsize(p) // 4096 * 4096 for p in my_paths]
+    scratch = np.zeros(max(sizes), dtype=np.uint8)          # touched: no page faults while timing
+    buf = cpp.gds_device_buffer(scratch.ctypes.data, scratch.size, False)
+    reader = cpp.Reader(-1, threads, 4 << 20, 2, io_mode=nat.IO_DIRECT)
+    t0 = time.perf_counter()
+    reqs = [reader.submit(p, 0, n, buf, 0) for p, n in zip(my_paths, sizes)]
+    for r in reqs:
+        reader.wait(r)
+    dt = time.perf_counter() - t0
+    reader.close()
+    return dt
 
 
 def other_kernels(device: str, peak: float) -> dict:
@@ -504,43 +759,118 @@ def other_kernels(device: str, peak: float) -> dict:
     return out
 
 
-def storage_roofline(paths, my_paths, rank, barrier, max_over_ranks) -> dict:
-    """Cold O_DIRECT read bandwidth of the same files with the same thread count, into host
-    memory (the role fio plays where it is installed): the ceiling for a cold end-to-end load."""
-    from fastsafetensors_b200 import _native as nat
-    from fastsafetensors_b200 import cpp
-    from tests import synth
-    import numpy as np
+# ------------------------------------------------------------------------------------------
+# upstream's CUDA path, timed inside the same ranks on the same files
+# ------------------------------------------------------------------------------------------
+REF_DIR = os.path.join(ROOT, "oracle", "_ref")
+REFERENCE_CUDA_LIMIT_S = 300.0
 
-    if rank == 0:
-        synth.drop_page_cache(paths)
-    barrier()
-    total = sum(os.path.getsize(p) for p in paths)
-    scratch = np.empty(max([os.path.getsize(p) for p in my_paths] or [1]), dtype=np.uint8)
-    buf = cpp.gds_device_buffer(scratch.ctypes.data, scratch.size, False)
-    reader = cpp.Reader(-1, 16, 4 << 20, 2, io_mode=nat.IO_DIRECT)
-    barrier()
-    t0 = time.perf_counter()
-    for p in my_paths:
-        n = os.path.getsize(p) // 4096 * 4096
-        reader.wait(reader.submit(p, 0, n, buf, 0))
-    barrier()
-    dt = max_over_ranks(time.perf_counter() - t0)
-    reader.close()
-    return {"cold_direct_gbs": round(total / dt / GB, 3), "threads_per_rank": 16, "block": "4 MiB",
-            "tool": "native reader, O_DIRECT, host destination (fio is not installed)"}
+
+def reference_cuda_phase(wl: Workload, owners, pg, rank, world, device, barrier, max_over_ranks,
+                         line_so_far) -> dict:
+    """Upstream's loader with ``device=cuda:r`` and ``nogds=True`` (buffered pread + synchronous
+    cudaMemcpy per chunk), the checkpoint's plan served tensor by tensor through
+    ``get_sharded`` / ``get_tensor`` / ``push_tensor`` (tensor_factory.py:58-192: with N > 1 one
+    NCCL scatter or broadcast and one device synchronisation per tensor; with one rank upstream
+    returns whole tensors, so N = 1 times the load alone).  One cold and one warm end-to-end step
+    and the time of the shuffle phase alone.
+
+    A watchdog ends the process (after rank 0 has printed the line it has so far) if upstream's
+    code does not come back within the limit."""
+    import torch
+
+    from tests import synth
+
+    if not os.path.exists(os.path.join(REF_DIR, "fastsafetensors", "__init__.py")):
+        return {"unavailable": "oracle/_ref is not built (oracle/build_ref.sh)"}
+
+    def give_up():
+        if line_so_far is not None:
+            line_so_far["reference_cuda"] = {"unavailable": f"upstream's CUDA path did not finish within "
+                                                            f"{REFERENCE_CUDA_LIMIT_S:.0f} s"}
+            emit(line_so_far)
+        os._exit(0)
+
+    dog = threading.Timer(REFERENCE_CUDA_LIMIT_S, give_up)
+    dog.daemon = True
+    dog.start()
+    try:
+        sys.path.insert(0, REF_DIR)
+        import fastsafetensors as ref
+
+        out = {}
+        for label, cold in (("cold", True), ("warm", False)):
+            if cold and rank == 0:
+                synth.drop_page_cache(wl.paths)
+            torch.cuda.synchronize()
+            barrier()
+            t0 = time.perf_counter()
+            loader = ref.SafeTensorsFileLoader(pg if pg is not None else ref.SingleGroup(), device, nogds=True)
+            loader.add_filenames(owners)
+            fb = loader.copy_files_to_device()
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            keep = []
+            for name, action in wl.plan.items():
+                if action[0] == "shard":
+                    keep.append(fb.get_sharded(name, action[1]))
+                elif action[0] == "replicate":
+                    keep.append(fb.get_tensor(name))
+                else:
+                    keep.append(fb.push_tensor(name, action[1]))
+            torch.cuda.synchronize()
+            barrier()
+            t2 = time.perf_counter()
+            total, shuffle = max_over_ranks(t2 - t0), max_over_ranks(t2 - t1)
+            out[label] = {"e2e_gbs": round(wl.data_bytes / total / GB, 3), "s_per_step": round(total, 3),
+                          "shuffle_phase_s": round(shuffle, 4),
+                          "shuffle_phase_gbs": round(wl.data_bytes / shuffle / GB, 2)}
+            del keep
+            fb.close()
+            loader.close()
+            torch.cuda.empty_cache()
+        out["what"] = (f"upstream fastsafetensors 0.3.2 (oracle/_ref), device cuda:r, nogds, {world} rank(s) over "
+                       f"NCCL, library defaults; files -> HBM, then every tensor of the plan"
+                       + (" (one rank: upstream hands out whole tensors, no sharding)" if world == 1 else ""))
+        return out
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {e}"}
+    finally:
+        dog.cancel()
+        if REF_DIR in sys.path:
+            sys.path.remove(REF_DIR)
 
 
 # ------------------------------------------------------------------------------------------
 # upstream's CPU path (the checker's build in oracle/_ref), timed on the host cores
 # ------------------------------------------------------------------------------------------
-REF_DIR = os.path.join(ROOT, "oracle", "_ref")
-
-
 def _numa_nodes() -> int:
     import glob
 
     return max(1, len(glob.glob("/sys/devices/system/node/node[0-9]*")))
+
+
+def _host_cores_and_l2_kb():
+    """Physical cores and their summed L2 capacity in KiB, from sysfs (what upstream's perf tool
+    reads, perf/fastsafetensors_perf/perf.py:345-365); (None, None) if unreadable."""
+    import glob
+
+    cores, l2_kb = set(), 0
+    try:
+        for cpudir in glob.glob("/sys/devices/system/cpu/cpu[0-9]*"):
+            if not os.path.exists(f"{cpudir}/topology/core_id"):
+                continue
+            size = open(f"{cpudir}/cache/index2/size").read().strip()
+            if not size.endswith("K"):
+                return None, None
+            core = (open(f"{cpudir}/topology/physical_package_id").read().strip(),
+                    open(f"{cpudir}/topology/core_id").read().strip())
+            if core not in cores:
+                cores.add(core)
+                l2_kb += int(size[:-1])
+    except (OSError, ValueError):
+        return None, None
+    return (len(cores) or None), (l2_kb or None)
 
 
 def _reference_settings(kind: str, paths, world: int):
@@ -553,11 +883,9 @@ def _reference_settings(kind: str, paths, world: int):
     bytes / ranks / threads rounded up to the bounce size, so that every thread has a block."""
     if kind == "defaults":
         return {}, {}
-    from fastsafetensors_b200 import tune
-
-    topo = tune.HostTopology.probe(None)
-    threads = max(1, topo.physical_cores or os.cpu_count() or 1)
-    bbuf_kb = topo.l2_kb or 16 * 1024
+    cores, l2_kb = _host_cores_and_l2_kb()
+    threads = max(1, cores or os.cpu_count() or 1)
+    bbuf_kb = l2_kb or 16 * 1024
     block = max(1, sum(os.path.getsize(p) for p in paths) // world // threads)
     unit = bbuf_kb * 1024
     if block % unit:
@@ -569,7 +897,15 @@ def _reference_rank(rank: int, world: int, paths, plan_items, phases, port: int,
                     settings: str = "defaults") -> None:
     """One gloo rank running UPSTREAM's loader on device "cpu": files owned round-robin, every
     tensor requested by the plan (get_sharded / get_tensor / push_tensor).  ``settings``:
-    ``defaults``, ``tuned`` or ``best`` (one untimed step with each, the faster one is timed)."""
+    ``defaults``, ``tuned`` or ``best`` (one untimed step with each, the faster one is timed).
+
+    Phases, each ``(label, kind, steps, warmup, budget_s)``:
+    ``kind == "e2e_cold" / "e2e_warm"``: loader construction -> copy_files_to_device -> every
+    tensor of the plan, page cache dropped before the step or not;
+    ``kind == "resident"``: the images are loaded once, untimed, and kept (auto_mem_delete off);
+    a step is every tensor of the plan from the resident images -- upstream's shuffle phase
+    (perf.py:609-637, t2 -> t3).  If the first step shows that the steps would not fit
+    ``budget_s``, the phase goes on with the first files only and says so."""
     sys.path.insert(0, REF_DIR)
     import torch
     import torch.distributed as dist
@@ -599,17 +935,7 @@ def _reference_rank(rank: int, world: int, paths, plan_items, phases, port: int,
             dist.broadcast_object_list(box, src=0)
         return box[0]
 
-    def one_step(kind: str, n_files: int, cold: bool):
-        use = sorted(paths)[:n_files]
-        loader_kw, copy_kw = _reference_settings(kind, use, world)
-        if cold and rank == 0:
-            synth.drop_page_cache(use)
-        barrier()
-        t0 = time.perf_counter()
-        loader = ref.SafeTensorsFileLoader(pg if pg is not None else ref.SingleGroup(), "cpu", nogds=True,
-                                           **loader_kw)
-        loader.add_filenames(synth.owners(use, world))
-        fb = loader.copy_files_to_device(**copy_kw)
+    def serve_plan(fb):
         present = set(fb.key_to_rank_lidx)
         keep = []
         for name, action in plan_items:
@@ -621,9 +947,27 @@ def _reference_rank(rank: int, world: int, paths, plan_items, phases, port: int,
                 keep.append(fb.get_tensor(name))
             else:
                 keep.append(fb.push_tensor(name, action[1]))
+        return keep
+
+    def open_and_copy(kind: str, use):
+        loader_kw, copy_kw = _reference_settings(kind, use, world)
+        loader = ref.SafeTensorsFileLoader(pg if pg is not None else ref.SingleGroup(), "cpu", nogds=True,
+                                           **loader_kw)
+        loader.add_filenames(synth.owners(use, world))
+        fb = loader.copy_files_to_device(**copy_kw)
+        nbytes = sum(m.size_bytes - m.header_length for m, _ in loader.meta.values())
+        return loader, fb, nbytes
+
+    def e2e_step(kind: str, n_files: int, cold: bool):
+        use = sorted(paths)[:n_files]
+        if cold and rank == 0:
+            synth.drop_page_cache(use)
+        barrier()
+        t0 = time.perf_counter()
+        loader, fb, nbytes = open_and_copy(kind, use)
+        keep = serve_plan(fb)
         barrier()
         dt = time.perf_counter() - t0
-        nbytes = sum(m.size_bytes - m.header_length for m, _ in loader.meta.values())
         del keep
         fb.close()
         loader.close()
@@ -632,33 +976,59 @@ def _reference_rank(rank: int, world: int, paths, plan_items, phases, port: int,
     results = {}
     chosen = None if settings == "best" else settings
     tried = {}
-    for label, cold, steps, warmup, budget_s in phases:
+    for label, kind, steps, warmup, budget_s in phases:
         n_files = len(paths)
-        last_dt = None
-        if chosen is None:
-            # one untimed step with each setting over the whole checkpoint; they double as warm-up
-            trial = {}
-            for kind in ("defaults", "tuned"):
-                trial[kind] = one_step(kind, n_files, cold)
-                tried[kind] = round(trial[kind][1] / trial[kind][0] / GB, 3)
-            chosen = agreed(max(tried, key=tried.get))
-            last_dt = trial[chosen][0]
-            if steps == 0:      # the trial of the faster setting is the sample
-                results[label] = {"seconds": [trial[chosen][0]], "bytes": [trial[chosen][1]], "files": n_files}
-                continue
-        else:
-            for _ in range(warmup):
-                last_dt, _ = one_step(chosen, n_files, cold)
-        # bounded sample: if the timed steps would not fit the phase's budget, go on with the
-        # first files only (rank 0 decides, everyone follows)
-        if last_dt is not None and last_dt * steps > budget_s:
-            n_files = max(1, int(len(paths) * budget_s / (last_dt * steps)))
-        n_files = agreed(n_files)
-        samples = [one_step(chosen, n_files, cold) for _ in range(steps)]
-        results[label] = {"seconds": [s_[0] for s_ in samples], "bytes": [s_[1] for s_ in samples],
-                          "files": n_files}
+        if kind in ("e2e_cold", "e2e_warm"):
+            cold = kind == "e2e_cold"
+            if chosen is None:
+                # one untimed step with each setting over the whole checkpoint; they double as warm-up
+                trial = {}
+                for k in ("defaults", "tuned"):
+                    trial[k] = e2e_step(k, n_files, cold)
+                    tried[k] = round(trial[k][1] / trial[k][0] / GB, 3)
+                chosen = agreed(max(tried, key=tried.get))
+                if steps == 0:      # the trial of the faster setting is the sample
+                    results[label] = {"seconds": [trial[chosen][0]], "bytes": [trial[chosen][1]], "files": n_files}
+                    continue
+            else:
+                for _ in range(warmup):
+                    e2e_step(chosen, n_files, cold)
+            samples = [e2e_step(chosen, n_files, cold) for _ in range(steps)]
+            results[label] = {"seconds": [s_[0] for s_ in samples], "bytes": [s_[1] for s_ in samples],
+                              "files": n_files}
+            continue
+        # resident phase
+        use_kind = chosen or "tuned"
+        secs, nb = [], 0
+        while True:
+            loader, fb, nb = open_and_copy(use_kind, sorted(paths)[:n_files])
+            fb.auto_mem_delete = False          # keep the images: every step starts from them
+            barrier()
+            t0 = time.perf_counter()
+            keep = serve_plan(fb)
+            barrier()
+            first = time.perf_counter() - t0
+            del keep
+            fit = agreed(first * (steps + warmup) <= budget_s or n_files == 1)
+            if fit:
+                break
+            fb.close()
+            loader.close()
+            n_files = agreed(max(1, min(n_files - 1, int(n_files * budget_s / (first * (steps + warmup))))))
+        for i in range(max(0, warmup - 1) + steps):
+            barrier()
+            t0 = time.perf_counter()
+            keep = serve_plan(fb)
+            barrier()
+            dt = time.perf_counter() - t0
+            del keep
+            if i >= max(0, warmup - 1):
+                secs.append(dt)
+        fb.close()
+        loader.close()
+        results[label] = {"seconds": secs, "bytes": [nb] * len(secs), "files": n_files}
     results["settings"] = {"used": chosen, "tried_gbs": tried,
-                           "kwargs": [dict(d) for d in _reference_settings(chosen, sorted(paths), world)]}
+                           "kwargs": [dict(d) for d in _reference_settings(chosen or "tuned", sorted(paths), world)]}
     if rank == 0:
         with open(out_path, "w") as f:
             json.dump(results, f)
@@ -666,18 +1036,18 @@ def _reference_rank(rank: int, world: int, paths, plan_items, phases, port: int,
         dist.destroy_process_group()
 
 
-def run_reference(spec, paths, tp: int, phases, timeout_s: float = 900.0, settings: str = "defaults") -> dict:
+def run_reference(wl: Workload, paths, phases, timeout_s: float = 900.0, settings: str = "defaults") -> dict:
+    import socket
     import tempfile
 
     import torch.multiprocessing as mp
 
     if not os.path.exists(os.path.join(REF_DIR, "fastsafetensors", "__init__.py")):
         raise FileNotFoundError("oracle/_ref is missing (build it with oracle/build_ref.sh)")
-    plan_items = list(plan_for(spec, tp).items())
+    plan_items = list(wl.plan.items())
+    tp = wl.tp
     with tempfile.TemporaryDirectory() as tmp:
         out_path = os.path.join(tmp, "times.json")
-        import socket
-
         with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:   # a port that is free now
             sock.bind(("127.0.0.1", 0))
             port = sock.getsockname()[1]
@@ -695,135 +1065,115 @@ def run_reference(spec, paths, tp: int, phases, timeout_s: float = 900.0, settin
         return json.load(open(out_path))
 
 
-def cpu_baseline(spec, paths, tp: int) -> dict:
-    """Upstream on the host cores, one cold and one warm pass over the same checkpoint."""
-    t, failure = None, None
-    for settings, phases in (("best", [("cold", True, 0, 0, 1e9), ("warm", False, 1, 0, 1e9)]),
-                             ("defaults", [("cold", True, 1, 0, 1e9), ("warm", False, 1, 0, 1e9)])):
-        try:
-            t = run_reference(spec, paths, tp, phases, timeout_s=300.0, settings=settings)
-            break
-        except Exception as e:  # noqa: BLE001
-            failure = f"failed: {type(e).__name__}: {e}"
-    if t is None:
-        return {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference", "sample": failure}
-    cold, warm = t["cold"]["seconds"][0], t["warm"]["seconds"][0]
-    return {"value": round(spec.data_bytes / cold / GB, 3), "unit": "GB/s", "cores": os.cpu_count(),
-            "kind": "reference",
-            "sample": f"upstream fastsafetensors 0.3.2, device cpu, nogds, {tp} gloo ranks, whole "
-                      f"{spec.name} checkpoint once with the page cache dropped ({cold:.2f} s) and "
-                      f"once warm ({warm:.2f} s); the faster of library defaults (one request per "
-                      f"file) and the rule of upstream's perf tool (a block per thread), cold GB/s: "
-                      f"{t['settings']['tried_gbs']}, used: {t['settings']['used']} {t['settings']['kwargs']}",
-            "warm_value": round(spec.data_bytes / warm / GB, 3), "settings": t["settings"],
-            "numa_nodes": _numa_nodes()}
-
-
-def reference_cuda_subprocess(args) -> dict:
-    """Run ``--impl reference-cuda`` in a child process (its own CUDA context and allocator)."""
-    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference-cuda", "--config", args.config,
-           "--scale", args.scale, "--dir", args.dir, "--layers", str(args.layers)]
+def cpu_baseline(wl: Workload) -> dict:
+    """Upstream on the host cores on a bounded sample: the first file of the checkpoint, loaded
+    cold from disk to the shards of all ranks, once with each of upstream's two settings."""
+    sample = wl.paths[:1]
     try:
-        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
-        line = [l for l in proc.stdout.splitlines() if l.startswith("{")]
-        return json.loads(line[-1]) if line else {"unavailable": (proc.stderr or "no output")[-300:]}
+        t = run_reference(wl, sample, [("cold", "e2e_cold", 0, 0, 1e9)], timeout_s=300.0, settings="best")
     except Exception as e:  # noqa: BLE001
-        return {"unavailable": f"{type(e).__name__}: {e}"}
+        return {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference",
+                "sample": f"failed: {type(e).__name__}: {e}"}
+    cold, nbytes = t["cold"]["seconds"][0], t["cold"]["bytes"][0]
+    return {"value": round(nbytes / cold / GB, 3), "unit": "GB/s", "cores": os.cpu_count(),
+            "kind": "reference",
+            "sample": f"upstream fastsafetensors 0.3.2, device cpu, nogds, {wl.tp} gloo ranks, the first file of "
+                      f"the {wl.spec.name} checkpoint ({nbytes} data bytes) from disk to shards with the page "
+                      f"cache dropped ({cold:.2f} s); the faster of library defaults (one request per file) "
+                      f"and the rule of upstream's perf tool (a block per thread), cold GB/s: "
+                      f"{t['settings']['tried_gbs']}, used: {t['settings']['used']} {t['settings']['kwargs']}",
+            "settings": t["settings"], "numa_nodes": _numa_nodes()}
 
 
 def reference_arm(args) -> dict:
-    from tests import synth
-
     rank, _, world = dist_env()
     if rank != 0:
         return {}
-    spec = load_spec(args)
-    tp = spec.tp if world == 1 else world
-    paths = prepare_files(spec, args.dir, 0, lambda: None)
-    phases = [("cold", True, args.steps, 1, args.ref_budget), ("warm", False, min(args.steps, 3), 1, 40.0)]
+    wl = Workload(args, world)
+    wl.write(0, lambda: None)
+    warmup = max(3, args.warmup)
+    cold_steps = wl.e2e_steps(args)
+    phases = [("cold", "e2e_cold", cold_steps, 1, 1e9), ("warm", "e2e_warm", min(args.steps, 3), 1, 1e9),
+              ("resident", "resident", args.steps, warmup, args.ref_budget)]
+    if args.no_e2e:
+        phases = phases[2:]
     try:
-        t = run_reference(spec, paths, tp, phases, timeout_s=600.0, settings=args.ref_settings)
+        t = run_reference(wl, wl.paths, phases, timeout_s=800.0, settings=args.ref_settings)
     except Exception as e:  # noqa: BLE001
         if args.ref_settings == "defaults":
             raise
         sys.stderr.write(f"[bench] reference arm with settings {args.ref_settings!r} failed "
                          f"({type(e).__name__}: {e}); running upstream's defaults\n")
-        t = run_reference(spec, paths, tp, phases, timeout_s=600.0, settings="defaults")
+        t = run_reference(wl, wl.paths, phases, timeout_s=800.0, settings="defaults")
 
     def rate(ph):
         return sum(ph["bytes"]) / sum(ph["seconds"]) / GB
 
-    cold = sum(t["cold"]["seconds"]) / len(t["cold"]["seconds"])
-    v = round(rate(t["cold"]), 3)
-    sample = (f"upstream fastsafetensors 0.3.2 (oracle/_ref), device cpu, nogds, {tp} gloo ranks on "
-              f"{os.cpu_count()} cores, {t['cold']['files']} of {len(paths)} files of the {spec.name} "
-              f"checkpoint per step, page cache dropped before every step; settings "
-              f"{t['settings']['used']} {t['settings']['kwargs']} (cold GB/s of one untimed step each: "
-              f"{t['settings']['tried_gbs']})")
-    return {
+    res = t["resident"]
+    res_s = sum(res["seconds"]) / len(res["seconds"])
+    v = round(rate(res), 3)
+    whole = res["files"] == len(wl.paths)
+    used = f"settings {t['settings']['used']} {t['settings']['kwargs']}"
+    sample = (f"upstream fastsafetensors 0.3.2 (oracle/_ref), device cpu, nogds, {wl.tp} gloo ranks on "
+              f"{os.cpu_count()} cores; file images resident in host memory -> every tensor of the plan through "
+              f"get_sharded / get_tensor / push_tensor (upstream's shuffle phase), "
+              + ("whole checkpoint per step" if whole else
+                 f"first {res['files']} of {len(wl.paths)} files per step (the whole checkpoint would not fit "
+                 f"{args.ref_budget:.0f} s)") + f"; {used}")
+    out = {
         "impl": "reference",
-        "metric": "safetensors->HBM tensor-parallel load throughput",
-        "value": v, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": 1,
-        "ms_per_step": round(cold * 1e3, 2), "higher_is_better": True, "scaling": "strong",
+        "metric": METRIC,
+        "value": v, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(res_s * 1e3, 2), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": f"{spec.name} ({args.scale}): {len(spec.tensors)} tensors, {len(paths)} files, "
-                               f"{spec.data_bytes} data bytes, tensor-parallel {tp}-way, host memory", "tp": tp},
+        "config": wl.config_block(),
+        "notes": {"value_phase": "file images resident in host memory -> shards in host memory "
+                                 "(upstream's shuffle phase, gloo)",
+                  "whole_checkpoint_per_step": whole},
         "cpu_baseline": {"value": v, "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference",
                          "sample": sample, "numa_nodes": _numa_nodes(), "settings": t["settings"]},
-        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                "page_cache": "dropped before every step"},
-        "e2e_warm": {"value": round(rate(t["warm"]), 3), "unit": "GB/s", "files": t["warm"]["files"]},
         "gpu_launches": 0,
     }
+    if "cold" in t:
+        cold = t["cold"]
+        out["e2e"] = {"value": round(rate(cold), 3), "unit": "GB/s", "h2d_bytes_per_step": 0,
+                      "d2h_bytes_per_step": 0, "steps": len(cold["seconds"]), "warmup": 1,
+                      "s_per_step": round(sum(cold["seconds"]) / len(cold["seconds"]), 3),
+                      "page_cache": "dropped before every step",
+                      "what": "files on disk -> shards in host memory, whole checkpoint per step; "
+                              f"cold GB/s of one untimed step with each of upstream's settings: "
+                              f"{t['settings']['tried_gbs']}; {used}"}
+        out["e2e_warm"] = {"value": round(rate(t["warm"]), 3), "unit": "GB/s", "steps": len(t["warm"]["seconds"])}
+    else:
+        out["e2e"] = {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    return out
 
 
-def reference_cuda_arm(args) -> dict:
-    """Upstream's own CUDA path (nogds: buffered pread + synchronous cudaMemcpy per chunk) on
-    one GPU: files -> HBM, every tensor instantiated.  One rank cannot shard, so this times the
-    load only; it is reported beside the b200 arm, not as the reference arm."""
-    sys.path.insert(0, REF_DIR)
-    import torch
+_json_fd = None
 
-    import fastsafetensors as ref
-    from tests import synth
 
-    spec = load_spec(args)
-    paths = prepare_files(spec, args.dir, 0, lambda: None)
-    out = {}
-    for label, cold in (("cold", True), ("warm", False)):
-        if cold:
-            synth.drop_page_cache(paths)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        loader = ref.SafeTensorsFileLoader(ref.SingleGroup(), "cuda:0", nogds=True)
-        loader.add_filenames({0: paths})
-        fb = loader.copy_files_to_device()
-        keep = [fb.get_tensor(k) for k in fb.key_to_rank_lidx]
-        torch.cuda.synchronize()
-        out[label] = round(spec.data_bytes / (time.perf_counter() - t0) / GB, 3)
-        del keep
-        fb.close()
-        loader.close()
-    return {"impl": "reference-cuda", "unit": "GB/s", "cold": out["cold"], "warm": out["warm"],
-            "what": "upstream fastsafetensors 0.3.2, device cuda:0, nogds, one rank, library defaults; "
-                    "files -> HBM and get_tensor of every key (no sharding with one rank)"}
+def emit(line: dict) -> None:
+    os.write(_json_fd, (json.dumps(line) + "\n").encode())
 
 
 def main() -> None:
+    global _json_fd
     args = parse_args()
     # stdout carries the one JSON line and nothing else: libraries that print to file
     # descriptor 1 (NCCL's version banner, for one) are sent to stderr for the whole run
     sys.stdout.flush()
-    json_fd = os.dup(1)
+    _json_fd = os.dup(1)
     os.dup2(2, 1)
-    if args.impl == "reference-cuda":
-        out = reference_cuda_arm(args)
-    else:
-        out = reference_arm(args) if args.impl == "reference" else b200_arm(args)
+    out = reference_arm(args) if args.impl == "reference" else b200_arm(args)
     sys.stdout.flush()
+    parity_ok = True
     if out:
-        os.write(json_fd, (json.dumps(out) + "\n").encode())
-    os.close(json_fd)
+        parity_ok = out.get("parity", {}).get("ok", out.get("parity_ok", True))
+        if "parity_ok" not in out:
+            emit(out)
+    os.close(_json_fd)
+    if not parity_ok:
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -202,6 +202,23 @@ def make_ops(ops: Sequence[Tuple[int, int, int, int, int, int]]):
     return arr
 
 
+class PackedOps:
+    """An op table packed once for repeated launches: a contiguous ``(n, 6)`` uint64 array
+    (one ``fst_copy2d_t`` per row, filled without a Python loop per field) and the pointer the
+    C entry points take."""
+
+    def __init__(self, ops: Sequence[Tuple[int, int, int, int, int, int]]):
+        import numpy as np
+
+        self.array = np.ascontiguousarray(np.array(ops, dtype=np.uint64).reshape(-1, 6))
+        self.count = int(self.array.shape[0])
+        self.pointer = self.array.ctypes.data_as(POINTER(Copy2D))
+
+
+def pack_ops(ops: Sequence[Tuple[int, int, int, int, int, int]]) -> PackedOps:
+    return PackedOps(ops)
+
+
 def gather(ops: Sequence[Tuple[int, int, int, int, int, int]], stream: int,
            src_span: Tuple[int, int] = (0, 0), dst_span: Tuple[int, int] = (0, 0)) -> None:
     """Device gather: one launch for all ops on ``stream`` (``fst_gather``)."""

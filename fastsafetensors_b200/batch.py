@@ -10,11 +10,12 @@ exchange out explicitly:
 * ``BatchLayout`` assigns every requested (tensor, destination rank) pair a 256-byte aligned
   slot inside the region ``[owner -> destination]``; every rank computes the same layout from the
   headers alone (all ranks parse all headers);
-* the owner fills its ``W`` outgoing regions with ONE gather launch per file
+* the owner fills its ``W`` outgoing regions with one gather launch per chunk
   (``fill_ops``: shards as strided copies, replicated and pushed tensors as flat copies), writing
   its own region straight into the receive buffer;
-* one ``all_to_all_single`` with the region sizes as split sizes moves everything; results are
-  typed views of the receive buffer.
+* one ``all_to_all_single`` per chunk with the region sizes as split sizes moves the data while
+  the next chunk is being packed (and, with deferred reads, read); results are typed views of
+  the receive buffer.
 """
 
 from __future__ import annotations
@@ -139,109 +140,207 @@ class BatchLayout:
         return out
 
 
+def cut_into_chunks(fb, requests: "Dict[str, Action]", world: int, chunk_bytes: int) -> List[List[str]]:
+    """Order of work for one exchange: requests grouped by *round* (round j = the j-th file of
+    every owner rank, i.e. the files the ranks read at the same time), each round cut, in request
+    order, into chunks in which no owner sends more than ``chunk_bytes``.  Every rank computes the
+    same chunks from the headers alone."""
+    by_round: Dict[int, List[str]] = {}
+    for name in requests:
+        _, lidx = fb._get_rank_lidx(name)
+        by_round.setdefault(lidx, []).append(name)
+    chunks: List[List[str]] = []
+    for lidx in sorted(by_round):
+        volume: Dict[int, int] = {}
+        cur: List[str] = []
+        for name in by_round[lidx]:
+            rank, _ = fb._get_rank_lidx(name)
+            frame = fb.rank_loaders[rank][lidx].metadata.tensors[name]
+            nbytes = frame.data_offsets[1] - frame.data_offsets[0]
+            cost = nbytes * (world if requests[name][0] == "replicate" else 1)
+            if cur and volume.get(rank, 0) + cost > chunk_bytes:
+                chunks.append(cur)
+                cur, volume = [], {}
+            cur.append(name)
+            volume[rank] = volume.get(rank, 0) + cost
+        if cur:
+            chunks.append(cur)
+    return chunks
+
+
+@dataclass
+class _Chunk:
+    names: List[str]
+    layout: BatchLayout
+    recv_base: int                 # offset of this chunk's part of the receive buffer
+    recv_bytes: int
+    send_bytes: int
+    launches: Optional[list] = None    # [(op array, count, dst base, dst length, outgoing?)]
+    payload: int = 0
+
+
 class ShardExchange:
-    """One batch of requests, prepared once and runnable many times.
+    """The requests of one ``exchange`` / ``shard_locally`` call, prepared once, runnable many
+    times.
 
-    ``local=False``: this process is rank ``me`` of ``world``; ``run()`` packs what this rank owns
-    (gather kernel) and meets the other ranks in one ``all_to_all_single``; ``results()`` are the
-    tensors this rank receives.
+    The requests are cut into chunks (``cut_into_chunks``).  ``run()`` takes the chunks in order:
+    wait until this rank's file of the chunk has been read (a no-op unless the loader was asked
+    not to wait), pack what this rank owns with the gather kernel, start the chunk's
+    ``all_to_all_single`` asynchronously, go on to the next chunk.  So the gather of chunk k+1
+    runs while NVLink still carries chunk k, and with ``copy_files_to_device(wait=False)`` both
+    run while the reader is still filling the files of later rounds.  All chunks receive into
+    ONE buffer (allocated up front from the headers), sends go through a ring of two chunk-sized
+    buffers.
 
-    ``local=True``: this process owns every file and produces the data of all ``world``
-    destinations itself (no transport): ``run()`` is a single gather launch, ``results()`` is a
-    list with one ``{name: tensor}`` per destination rank.  This is the owner-side half of the
-    exchange run for all destinations at once, e.g. by a single-GPU process that prepares the
-    shards of a ``world``-way tensor-parallel group.
+    ``local=False``: this process is rank ``me`` of ``world``; ``results()`` are the tensors this
+    rank receives.  ``local=True``: this process owns every file and produces the data of all
+    ``world`` destinations itself (no transport, one gather launch per file); ``results()`` is a
+    list with one ``{name: tensor}`` per destination rank -- the owner-side half of the exchange
+    run for all destinations at once, e.g. by a single-GPU process that prepares the shards of a
+    ``world``-way tensor-parallel group.
     """
 
-    def __init__(self, fb, requests: "Dict[str, Action]", world: int, me: int, local: bool):
+    SEND_SLOTS = 2
+
+    def __init__(self, fb, requests: "Dict[str, Action]", world: int, me: int, local: bool,
+                 chunk_bytes: Optional[int] = None):
         import torch
 
+        self.fb, self.world, self.me, self.local = fb, world, me, local
+        self.requests = dict(requests)
+        self.names = list(requests)
+        self.frames: Dict[str, TensorFrame] = {}
+        self.device = next(l.device for ls in fb.rank_loaders.values() for l in ls)
+        if chunk_bytes is None:
+            chunk_bytes = (1 << 62) if local else default_chunk_bytes()
+        self.chunks: List[_Chunk] = []
+        recv_total, send_max = 0, 0
+        for names in cut_into_chunks(fb, requests, world, chunk_bytes):
+            lay = BatchLayout(world)
+            for name in names:
+                rank, lidx = fb._get_rank_lidx(name)
+                frame = fb.rank_loaders[rank][lidx].metadata.tensors[name]
+                self.frames[name] = frame
+                lay.add(name, frame, 0 if local else rank, requests[name])
+            recv = sum(lay.region_bytes[0]) if local else lay.recv_total(me)
+            send = 0 if local else sum(lay.send_sizes(me))
+            self.chunks.append(_Chunk(names, lay, recv_total, recv, send))
+            recv_total += recv
+            send_max = max(send_max, send)
+        torch_dev = "cpu" if self.device.is_cpu else self.device.as_str()
+        self.recv = torch.empty(recv_total, dtype=torch.uint8, device=torch_dev)
+        self.send_slot_bytes = send_max
+        self.send = None if local else torch.empty(self.SEND_SLOTS * send_max, dtype=torch.uint8,
+                                                    device=torch_dev)
+        self._slot_work: List[Optional[object]] = [None] * self.SEND_SLOTS
+        self.payload_bytes = 0          # bytes this rank's gather launches move (known after run)
+        # bytes this rank sends to other ranks over the whole exchange
+        self.egress_bytes = 0 if local else sum(
+            ch.layout.region_bytes[me][d] for ch in self.chunks for d in range(world) if d != me)
+
+    # ------------------------------------------------------------------ preparation of one chunk
+    def _prepare(self, index: int) -> _Chunk:
+        """Op tables of chunk ``index`` (built once).  Touches the tensors of the files this rank
+        owns in the chunk, which completes their reads if those were deferred."""
+        ch = self.chunks[index]
+        if ch.launches is not None:
+            return ch
         from . import _native as nat
 
-        self.fb, self.world, self.me, self.local = fb, world, me, local
-        self.names = list(requests)
-        self.layout = BatchLayout(world)
-        self.frames: Dict[str, TensorFrame] = {}
+        fb, lay, me = self.fb, ch.layout, self.me
         src_addr: Dict[str, int] = {}
-        self.device = next(l.device for ls in fb.rank_loaders.values() for l in ls)
-        for name in self.names:
+        for name in ch.names:
             rank, lidx = fb._get_rank_lidx(name)
-            loader = fb.rank_loaders[rank][lidx]
-            self.frames[name] = loader.metadata.tensors[name]
-            owner = 0 if local else rank
-            self.layout.add(name, self.frames[name], owner, requests[name])
-            if owner == me:
-                if name not in loader.tensors:
+            if self.local or rank == me:
+                loader = fb.rank_loaders[rank][lidx]
+                tensors = loader.tensors
+                if name not in tensors:
                     raise Exception(f"exchange: tensor {name} was not found, released? lidx={loader.lidx}")
-                src_addr[name] = loader.tensors[name].data_ptr()
-        torch_dev = "cpu" if self.device.is_cpu else self.device.as_str()
-        lay = self.layout
-        if local:
+                src_addr[name] = tensors[name].data_ptr()
+        recv_ptr = self.recv.data_ptr() + ch.recv_base
+        slot = index % self.SEND_SLOTS
+        if self.local:
             sizes = lay.region_bytes[0]
-            self.recv = torch.empty(sum(sizes), dtype=torch.uint8, device=torch_dev)
-            self.send = None
-            region = [self.recv.data_ptr() + sum(sizes[:d]) for d in range(world)]
+            region = [recv_ptr + sum(sizes[:d]) for d in range(self.world)]
         else:
-            self.recv = torch.empty(lay.recv_total(me), dtype=torch.uint8, device=torch_dev)
-            self.send = torch.empty(sum(lay.send_sizes(me)), dtype=torch.uint8, device=torch_dev)
-            region = [self.send.data_ptr() + lay.send_offset(me, d) for d in range(world)]
-            region[me] = self.recv.data_ptr() + lay.recv_offset(me, me)
-        mine = {n: f for n, f in self.frames.items() if n in src_addr}
+            send_ptr = self.send.data_ptr() + slot * self.send_slot_bytes
+            region = [send_ptr + lay.send_offset(me, d) for d in range(self.world)]
+            region[me] = recv_ptr + lay.recv_offset(me, me)
+        mine = {n: self.frames[n] for n in src_addr}
         ops = lay.fill_ops(me, mine, src_addr, region) if mine else []
-        self.payload_bytes = sum(o[2] * o[3] for o in ops)
-        lo, hi = self.recv.data_ptr(), self.recv.data_ptr() + self.recv.numel()
+        ch.payload = sum(o[2] * o[3] for o in ops)
+        lo, hi = recv_ptr, recv_ptr + ch.recv_bytes
         outgoing = [o for o in ops if not (lo <= o[1] < hi)]
         own = [o for o in ops if lo <= o[1] < hi]
-        # (ctypes op array, count, destination base, destination length) per launch.  What has
-        # to travel is packed first, so that the exchange can start while this rank's own
-        # region is still being packed (see run).
-        self.launches = []
-        if self.send is not None and outgoing:
-            self.launches.append((nat.make_ops(outgoing), len(outgoing), self.send.data_ptr(), self.send.numel()))
-        self.n_outgoing_launches = len(self.launches)
+        ch.launches = []
+        if outgoing:       # what has to travel is packed first, so that the exchange can start
+            ch.launches.append((nat.pack_ops(outgoing), len(outgoing), send_ptr, ch.send_bytes, True))
         if own:
-            self.launches.append((nat.make_ops(own), len(own), self.recv.data_ptr(), self.recv.numel()))
+            ch.launches.append((nat.pack_ops(own), len(own), recv_ptr, ch.recv_bytes, False))
+        return ch
 
-    def _launch_gathers(self, timing: Optional[list], which: Optional[slice] = None) -> None:
-        """Enqueue gather launches (all, or ``self.launches[which]``) on torch's current stream.
-        With ``timing`` a list, a pair of CUDA events brackets every launch and is appended."""
+    def _launch(self, ch: _Chunk, outgoing: bool, timing: Optional[list]) -> None:
+        """Enqueue the chunk's gather launches of one kind on torch's current stream.  With
+        ``timing`` a list, a pair of CUDA events brackets every launch and is appended."""
         from . import _native as nat
 
-        todo = self.launches if which is None else self.launches[which]
-        if self.device.is_cpu:
-            for arr, n, _, _ in todo:
-                nat.check(nat.lib.fst_gather_host(arr, n, 8), "fst_gather_host")
-            return
-        stream = self.fb.framework.current_stream(self.device)
-        for arr, n, base, length in todo:
+        for packed, n, base, length, is_out in ch.launches:
+            if is_out != outgoing:
+                continue
+            if self.device.is_cpu:
+                nat.check(nat.lib.fst_gather_host(packed.pointer, n, 8), "fst_gather_host")
+                continue
+            stream = self.fb.framework.current_stream(self.device)
             if timing is not None:
                 import torch
 
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record()
-            nat.check(nat.lib.fst_gather(arr, n, 0, 0, base, length, stream), "fst_gather")
+            nat.check(nat.lib.fst_gather(packed.pointer, n, 0, 0, base, length, stream), "fst_gather")
             if timing is not None:
                 b.record()
                 timing.append((a, b))
 
-    def run(self, timing: Optional[list] = None) -> None:
-        """Pack and exchange.  The outgoing regions are packed first and the ``all_to_all`` is
-        started asynchronously; this rank's own region is packed while the exchange runs (the two
-        write disjoint parts of the receive buffer); then the stream waits for the exchange."""
-        if self.local:
-            self._launch_gathers(timing)
-            return
+    # ------------------------------------------------------------------ the exchange
+    def run(self, timing: Optional[list] = None, after_chunk=None) -> None:
+        """Pack and exchange chunk by chunk.  ``after_chunk(names)`` is called when a chunk's
+        work has been queued (the caller releases file images there)."""
+        payload = 0
+        for index in range(len(self.chunks)):
+            ch = self._prepare(index)
+            payload += ch.payload
+            if self.local:
+                self._launch(ch, False, timing)
+            else:
+                self._run_chunk(index, ch, timing)
+            if after_chunk is not None:
+                after_chunk(ch.names)
+        self.payload_bytes = payload
+        for slot, work in enumerate(self._slot_work):
+            if work is not None:
+                work.wait()
+                self._slot_work[slot] = None
+
+    def _run_chunk(self, index: int, ch: _Chunk, timing: Optional[list]) -> None:
         import torch.distributed as dist
 
-        k = self.n_outgoing_launches
-        self._launch_gathers(timing, slice(0, k))
-        lay, me = self.layout, self.me
+        lay, me = ch.layout, self.me
+        slot = index % self.SEND_SLOTS
+        if self._slot_work[slot] is not None:
+            # the collective that last read this send slot must be done before the gather
+            # overwrites it (a stream-side wait for NCCL)
+            self._slot_work[slot].wait()
+            self._slot_work[slot] = None
+        self._launch(ch, True, timing)
         incoming = sum(lay.recv_sizes(me))
-        work = dist.all_to_all_single(self.recv[:incoming], self.send, lay.recv_sizes(me),
-                                      lay.send_sizes(me), group=self.fb.pg.real_pg, async_op=True)
-        self._launch_gathers(timing, slice(k, None))
-        work.wait()
+        recv = self.recv[ch.recv_base: ch.recv_base + incoming]
+        send = self.send[slot * self.send_slot_bytes: slot * self.send_slot_bytes + ch.send_bytes]
+        self._slot_work[slot] = dist.all_to_all_single(
+            recv, send, lay.recv_sizes(me), lay.send_sizes(me), group=self.fb.pg.real_pg, async_op=True)
+        # this rank's own region is packed while the exchange runs (disjoint part of the buffer)
+        self._launch(ch, False, timing)
 
+    # ------------------------------------------------------------------ results
     def _view(self, slot: Slot, off: int):
         from .frameworks._torch import TorchTensor, dtype_convert
 
@@ -251,15 +350,29 @@ class ShardExchange:
         return TorchTensor(self.device, frame.dtype, t)
 
     def results(self):
-        lay = self.layout
         if not self.local:
-            return {slot.name: self._view(slot, off) for slot, off in lay.received(self.me)}
-        out = []
-        sizes = lay.region_bytes[0]
-        for dst in range(self.world):
-            base = sum(sizes[:dst])
-            out.append({s.name: self._view(s, base + s.offset) for s in lay.slots[0][dst]})
-        return out
+            out = {}
+            for ch in self.chunks:
+                for slot, off in ch.layout.received(self.me):
+                    out[slot.name] = self._view(slot, ch.recv_base + off)
+            return out
+        per_dst: List[Dict[str, object]] = [{} for _ in range(self.world)]
+        for ch in self.chunks:
+            sizes = ch.layout.region_bytes[0]
+            for dst in range(self.world):
+                base = ch.recv_base + sum(sizes[:dst])
+                for s in ch.layout.slots[0][dst]:
+                    per_dst[dst][s.name] = self._view(s, base + s.offset)
+        return per_dst
+
+
+def default_chunk_bytes() -> int:
+    """Outgoing bytes per owner and chunk of a multi-rank exchange (``FST_B200_EXCHANGE_CHUNK_MB``,
+    default 1024): small enough that the gather of one chunk hides under the transfer of the
+    previous one, large enough that the collective's start-up cost does not show."""
+    import os
+
+    return max(1, int(os.environ.get("FST_B200_EXCHANGE_CHUNK_MB", "1024"))) << 20
 
 
 class PeerArenaUnavailable(RuntimeError):
@@ -454,10 +567,29 @@ class PeerShardExchange(ShardExchange):
         mine = {n: f for n, f in self.frames.items() if n in src_addr}
         ops = lay.fill_ops(me, mine, src_addr, region, rotate=True) if mine else []
         self.payload_bytes = sum(o[2] * o[3] for o in ops)
-        self.launches = [(nat.make_ops(ops), len(ops), 0, 0)] if ops else []
+        self.egress_bytes = sum(lay.region_bytes[me][d] for d in range(world) if d != me)
+        self.launches = [(nat.pack_ops(ops), len(ops))] if ops else []
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device.as_str())
 
-    def run(self, timing: Optional[list] = None) -> None:
+    def _launch_gathers(self, timing: Optional[list]) -> None:
+        import torch
+
+        from . import _native as nat
+
+        stream = self.fb.framework.current_stream(self.device)
+        for packed, n in self.launches:
+            if timing is not None:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+            nat.check(nat.lib.fst_gather(packed.pointer, n, 0, 0, 0, 0, stream), "fst_gather")
+            if timing is not None:
+                b.record()
+                timing.append((a, b))
+
+    def results(self):
+        return {slot.name: self._view(slot, off) for slot, off in self.layout.received(self.me)}
+
+    def run(self, timing: Optional[list] = None, after_chunk=None) -> None:
         import torch.distributed as dist
 
         group = self.fb.pg.real_pg
@@ -466,6 +598,8 @@ class PeerShardExchange(ShardExchange):
         dist.all_reduce(self._flag, group=group)      # every rank's kernel is complete
         if self.incoming:
             self.recv[: self.incoming].copy_(self._arena_view)
+        if after_chunk is not None:
+            after_chunk(self.names)
 
     def finish(self) -> None:
         """Kept for callers of the earlier interface; the arena now outlives the exchange."""

@@ -58,6 +58,12 @@ class B200FileCopier(CopierInterface):
             raise
         return gbuf
 
+    def drain(self) -> None:
+        """Wait for the read without instantiating anything (the image is about to be dropped)."""
+        if self.request is not None:
+            request, self.request = self.request, None
+            self.reader.wait(request)
+
     def wait_io(self, gbuf: gds_device_buffer, dtype: DType = DType.AUTO,
                 noalign: bool = False) -> Dict[str, Any]:
         if self.request is not None:

@@ -173,12 +173,16 @@ class FilesBufferOnDevice:
                  transport: Optional[str] = None) -> Dict[str, TensorBase]:
         """Serve many requests at once: ``{name: ("shard", dim) | ("replicate",) | ("push", r)}``.
 
-        Per batch (requests are cut into batches of at most ``max_batch_bytes`` outgoing bytes
-        per owner) every owner packs all it has to send with one gather launch per destination
-        buffer and all ranks meet in ONE ``all_to_all_single``; upstream issues a collective and
-        a device synchronisation per tensor (tensor_factory.py:143,186).  Results are views of
-        the batch's receive buffer.  For a pushed tensor only the destination rank gets an
-        entry.  Every rank must pass the same requests in the same order.
+        The requests are taken round by round (round j = the j-th file of every owner) and cut
+        into chunks of at most ``min(max_batch_bytes, FST_B200_EXCHANGE_CHUNK_MB)`` outgoing bytes
+        per owner.  Per chunk every owner packs what it has to send with one gather launch and
+        all ranks meet in ONE ``all_to_all_single``, started asynchronously so that the next
+        chunk is packed (and, after ``copy_files_to_device(wait=False)``, still being read)
+        while this one travels; upstream issues a collective and a device synchronisation per
+        tensor (tensor_factory.py:143,186).  Results are views of one receive buffer.  A file
+        image is released as soon as its last tensor has been packed.  For a pushed tensor only
+        the destination rank gets an entry.  Every rank must pass the same requests in the same
+        order.
 
         ``transport``: ``"nccl"`` packs into a send buffer and exchanges with
         ``all_to_all_single``; ``"peer"`` (CUDA devices of one machine) lets the gather kernel
@@ -189,7 +193,7 @@ class FilesBufferOnDevice:
         ``"nccl"``, on all ranks together, where peer mapping is refused.
         Default: the ``FST_B200_TRANSPORT`` environment variable, else ``"auto"``.
         """
-        from .batch import PeerArena, PeerArenaUnavailable, PeerShardExchange, ShardExchange
+        from .batch import PeerArena, PeerArenaUnavailable, PeerShardExchange, ShardExchange, default_chunk_bytes
 
         world, me = self.pg.size(), self.pg.rank()
         out: Dict[str, TensorBase] = {}
@@ -203,24 +207,31 @@ class FilesBufferOnDevice:
         fall_back = transport == "auto"
         if fall_back and PeerArena.known_unusable(self.pg, device):
             transport = "nccl"      # tried before on this group: all ranks know, nobody asks again
-        for names in self._batches(requests, world, max_batch_bytes):
-            batch = OrderedDict((n, requests[n]) for n in names)
-            ex = None
-            if transport in ("peer", "auto"):
-                try:
-                    ex = PeerShardExchange(self, batch, world, me)
-                except PeerArenaUnavailable as e:
-                    # raised by all ranks at the same call, so all take the same branch
-                    if not fall_back:
-                        raise
-                    logger.warning("exchange: %s; using the NCCL all-to-all", e)
-                    transport = "nccl"
-            if ex is None:
-                ex = ShardExchange(self, batch, world, me, local=False)
-            ex.run()
-            out.update(ex.results())
+
+        def release(names: List[str]) -> None:
             for name in names:
                 self._mark(*self.key_to_rank_lidx[name], name)
+
+        if transport in ("peer", "auto"):
+            done: List[str] = []
+            try:
+                for names in self._batches(requests, world, max_batch_bytes):
+                    batch = OrderedDict((n, requests[n]) for n in names)
+                    ex = PeerShardExchange(self, batch, world, me)
+                    ex.run(after_chunk=release)
+                    out.update(ex.results())
+                    done += names
+                return out
+            except PeerArenaUnavailable as e:
+                # raised by all ranks at the same call, so all take the same branch
+                if not fall_back:
+                    raise
+                logger.warning("exchange: %s; using the NCCL all-to-all", e)
+                requests = OrderedDict((n, a) for n, a in requests.items() if n not in set(done))
+        ex = ShardExchange(self, requests, world, me, local=False,
+                           chunk_bytes=min(max_batch_bytes, default_chunk_bytes()))
+        ex.run(after_chunk=release)
+        out.update(ex.results())
         return out
 
     def _batches(self, requests, world: int, max_batch_bytes: int) -> List[List[str]]:

@@ -104,10 +104,17 @@ class BaseSafeTensorsFileLoader:
                     self.frames.update(metadata.tensors)
 
     def copy_files_to_device(self, dtype: DType = DType.AUTO, use_buf_register: bool = True,
-                             max_copy_block_size: int = DEFAULT_MAX_COPY_BLOCK) -> FilesBufferOnDevice:
+                             max_copy_block_size: int = DEFAULT_MAX_COPY_BLOCK,
+                             wait: bool = True) -> FilesBufferOnDevice:
         """Start the reads of all files this rank owns, wait for them, and return the buffer
         object through which tensors are instantiated.  Files are taken in sorted path order;
-        a file's 1-based position is its id in send/recv tags (loader.py:121-168)."""
+        a file's 1-based position is its id in send/recv tags (loader.py:121-168).
+
+        ``wait=False`` (not in upstream) returns as soon as the reads are queued.  Each file is
+        then waited for by the first access to one of its tensors, so a caller that works
+        through the files in order -- ``FilesBufferOnDevice.exchange`` / ``as_dict`` /
+        ``shard_locally`` do -- packs and ships file k while the native reader is still filling
+        files k+1, k+2, ...; a failed read surfaces at that access instead of here."""
         self.framework.set_device(self.device)
         me = self.pg.rank()
         factories: Dict[int, List[LazyTensorFactory]] = {r: [] for r in range(self.pg.size())}
@@ -125,6 +132,9 @@ class BaseSafeTensorsFileLoader:
                 mine.append(factory)
         error: Optional[BaseException] = None
         for factory in mine:  # drain every request even if one fails
+            if not wait:
+                factory.defer_wait(dtype=dtype, noalign=False)
+                continue
             try:
                 factory.wait_io(dtype=dtype, noalign=False)
             except Exception as e:  # noqa: BLE001

@@ -42,7 +42,8 @@ class LazyTensorFactory:
         self.metadata = metadata
         self.device = device
         self.copier: Optional[CopierInterface] = copier if local_rank else None
-        self.tensors: Dict[str, TensorBase] = {}
+        self._tensors: Dict[str, TensorBase] = {}
+        self._deferred: Optional[tuple] = None   # (dtype, noalign) of a wait_io still to be done
         self.shuffled: Dict[str, TensorBase] = {}
         self.gbuf = None
         self.rank = rank                    # owner of the file
@@ -61,13 +62,57 @@ class LazyTensorFactory:
             logger.debug("submit_io: new buf, addr=0x%x", self.gbuf.get_base_address())
 
     def wait_io(self, dtype: DType = DType.AUTO, noalign: bool = False) -> None:
+        self._deferred = None
         if self.copier is not None and self.gbuf is not None:
-            self.tensors = self.copier.wait_io(self.gbuf, dtype=dtype, noalign=noalign)
+            copier, self.copier = self.copier, None
+            try:
+                self._tensors = copier.wait_io(self.gbuf, dtype=dtype, noalign=noalign)
+            except Exception:
+                self.free_dev_ptrs()
+                raise
             self.converted = dtype != DType.AUTO
-            self.copier = None
+
+    def defer_wait(self, dtype: DType = DType.AUTO, noalign: bool = False) -> None:
+        """Leave the read running: ``wait_io`` is done by the first access to ``tensors``
+        (``copy_files_to_device(wait=False)``), so that whoever consumes the files one after the
+        other overlaps its work on file k with the reads of files k+1, k+2, ..."""
+        if self.copier is not None and self.gbuf is not None:
+            self._deferred = (dtype, noalign)
+
+    @property
+    def pending(self) -> bool:
+        """True while this rank's read of the file has been started but not yet waited for."""
+        return self._deferred is not None
+
+    def ensure_loaded(self) -> None:
+        if self._deferred is not None:
+            dtype, noalign = self._deferred
+            self.wait_io(dtype=dtype, noalign=noalign)
+
+    @property
+    def tensors(self) -> Dict[str, TensorBase]:
+        """Tensors over this rank's image of the file (empty on ranks that hold no image).
+        Completes a deferred read first."""
+        if self._deferred is not None:
+            self.ensure_loaded()
+        return self._tensors
+
+    @tensors.setter
+    def tensors(self, value: Dict[str, TensorBase]) -> None:
+        self._tensors = value
 
     def free_dev_ptrs(self) -> None:
-        self.tensors = {}
+        if self._deferred is not None:
+            # the reader is still writing into the image: drain the request before the memory
+            # goes back to the allocator (errors of a read nobody wants any more are dropped)
+            self._deferred = None
+            copier, self.copier = self.copier, None
+            if copier is not None and self.gbuf is not None:
+                try:
+                    copier.drain()
+                except Exception:  # noqa: BLE001
+                    pass
+        self._tensors = {}
         if self.gbuf is not None and not isinstance(self.gbuf, DummyDeviceBuffer):
             logger.debug("free_dev_ptrs: delete buf, addr=0x%x", self.gbuf.get_base_address())
             self.framework.free_tensor_memory(self.gbuf, self.device)
@@ -84,6 +129,8 @@ class LazyTensorFactory:
             return False
         owner = self.rank == pg.rank()
         total = self.metadata.size_bytes - self.metadata.header_length
+        if owner:
+            self.ensure_loaded()
         if owner and self.gbuf is None:
             raise Exception(f"replicate: the image of {self.metadata.src} was already released")
         if not owner:

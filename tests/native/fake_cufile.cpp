@@ -22,7 +22,6 @@
 #include <cstdlib>
 #include <mutex>
 #include <set>
-#include <vector>
 
 namespace {
 
@@ -127,21 +126,25 @@ __attribute__((visibility("default"))) ssize_t cuFileRead(CUfileHandle_t fh, voi
         errno = EIO;
         return -1;
     }
-    std::vector<unsigned char> host(size);
+    // page-aligned bounce: the reader opens its files with O_DIRECT for cuFile
+    void *host = nullptr;
+    if (posix_memalign(&host, 4096, (size + 4095) / 4096 * 4096) != 0) return -1;
     size_t got = 0;
     while (got < size) {
-        const ssize_t c = pread(h->fd, host.data() + got, size - got, file_offset + (off_t)got);
+        const ssize_t c = pread(h->fd, (unsigned char *)host + got, size - got, file_offset + (off_t)got);
         if (c < 0) {
             if (errno == EINTR) continue;
+            std::free(host);
             return -1;
         }
         if (c == 0) break;  // end of file: a short count, as cuFileRead reports it
         got += (size_t)c;
+        if (got % 4096) break;  // a ragged count under O_DIRECT means end of file
     }
-    if (got &&
-        cudaMemcpy((unsigned char *)devPtr_base + devPtr_offset, host.data(), got,
-                   cudaMemcpyHostToDevice) != cudaSuccess)
-        return -1;
+    const bool ok = got == 0 || cudaMemcpy((unsigned char *)devPtr_base + devPtr_offset, host, got,
+                                           cudaMemcpyHostToDevice) == cudaSuccess;
+    std::free(host);
+    if (!ok) return -1;
     g_read_bytes += (int64_t)got;
     return (ssize_t)got;
 }

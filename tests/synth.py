@@ -267,13 +267,18 @@ def file_name(spec: CheckpointSpec, k: int, n: int) -> str:
     return f"{spec.name}-{k + 1:05d}-of-{n:05d}.safetensors"
 
 
-def write_checkpoint(spec: CheckpointSpec, out_dir: str, fsync: bool = True) -> List[str]:
-    """Write the checkpoint's files (skipping files that exist with the right size)."""
+def write_checkpoint(spec: CheckpointSpec, out_dir: str, fsync: bool = True,
+                     only_files: Optional[Sequence[int]] = None) -> List[str]:
+    """Write the checkpoint's files (skipping files that exist with the right size); with
+    ``only_files`` just the files of those indices.  Returns the paths written or found."""
     os.makedirs(out_dir, exist_ok=True)
     src = ValueSource(spec.seed, spec.dist)
     groups = partition(spec)
+    wanted = None if only_files is None else set(only_files)
     paths: List[str] = []
     for k, group in enumerate(groups):
+        if wanted is not None and k not in wanted:
+            continue
         entries: Dict[str, dict] = {}
         off = 0
         for i in group:

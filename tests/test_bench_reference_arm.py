@@ -15,20 +15,47 @@ REF = os.path.join(ROOT, "oracle", "_ref", "fastsafetensors", "__init__.py")
 @pytest.mark.skipif(not os.path.exists(REF), reason="oracle/_ref is not built (oracle/build_ref.sh)")
 def test_reference_arm_prints_one_contract_line(tmp_path):
     env = {k: v for k, v in os.environ.items() if not k.startswith("TORCHELASTIC_")}
-    proc = subprocess.run(
-        [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--scale", "tiny",
-         "--config", "llama2-13b", "--dir", str(tmp_path), "--steps", "1"],
-        capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    # run bench.py as __main__ and then report which of this repository's modules got imported
+    code = ("import runpy, sys; sys.argv = ['bench.py', '--impl', 'reference', '--scale', 'tiny', '--config', "
+            f"'llama2-13b', '--dir', {str(tmp_path)!r}, '--steps', '1']; "
+            f"runpy.run_path({os.path.join(ROOT, 'bench.py')!r}, run_name='__main__'); "
+            "sys.stderr.write('PRODUCT_MODULES=' + ','.join(sorted(m for m in sys.modules "
+            "if m.startswith('fastsafetensors_b200'))) + '\\n')")
+    proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=env,
+                          cwd=ROOT)
     assert proc.returncode == 0, proc.stderr[-2000:]
     lines = [l for l in proc.stdout.splitlines() if l.strip()]
     assert len(lines) == 1, proc.stdout
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and d["unit"] == "GB/s" and d["higher_is_better"] is True
-    assert d["value"] > 0 and d["gpu_launches"] == 0
-    assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0,
-                        "d2h_bytes_per_step": 0, "page_cache": "dropped before every step"}
+    assert d["value"] > 0 and d["gpu_launches"] == 0 and d["steps"] == 1 and d["warmup"] == 3
+    # value: upstream's shuffle phase from resident images; e2e: cold files -> shards
+    assert "resident" in d["notes"]["value_phase"] and d["notes"]["whole_checkpoint_per_step"] is True
+    assert d["e2e"]["value"] > 0 and d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
+    assert d["e2e"]["page_cache"] == "dropped before every step"
     cb = d["cpu_baseline"]
     assert cb["kind"] == "reference" and cb["value"] == d["value"] and cb["cores"] == os.cpu_count()
     # both of upstream's settings were tried and one of them was used
-    assert "defaults" in cb["sample"] and "tuned" in cb["sample"]
-    assert "tensor-parallel 4-way" in d["config"]["workload"]
+    assert set(cb["settings"]["tried_gbs"]) == {"defaults", "tuned"} and cb["settings"]["used"] in ("defaults", "tuned")
+    assert "tensor-parallel 4-way" in d["config"]["workload"] and d["config"]["tp"] == 4
+    # the arm must not import the product (and with it the native library)
+    assert "PRODUCT_MODULES=\n" in proc.stderr, proc.stderr[-500:]
+
+
+def test_both_arms_describe_the_same_workload():
+    """The ``config`` object is computed from the checkpoint alone, so both arms print the same."""
+    sys.path.insert(0, ROOT)
+    import argparse
+
+    import bench
+
+    args = argparse.Namespace(config=None, scale="tiny", layers=0, files=0, dir="/tmp/x", steps=20, e2e_steps=0)
+    one, eight = bench.Workload(args, 1), bench.Workload(args, 8)
+    assert one.spec.name == "llama2-13b" and one.tp == 4 and one.n_files == 3
+    assert eight.spec.name == "llama3-70b" and eight.tp == 8
+    args.files = 8
+    sub = bench.Workload(args, 8)
+    assert sub.n_files == 8 and len(sub.paths) == 8 and "first 8 of its 30 files" in sub.label
+    assert sub.data_bytes == sum(t.nbytes for t in sub.tensors) < eight.data_bytes
+    assert set(sub.plan) == {t.name for t in sub.tensors}
+    assert 2 <= sub.e2e_steps(args) <= 20

@@ -264,6 +264,52 @@ def test_shard_locally_produces_every_ranks_tensors(case, golden, case_files, le
     loader.close()
 
 
+def test_deferred_wait_overlaps_reads_with_packing(golden, case_files, leak_check):
+    """copy_files_to_device(wait=False): the reads are queued, each file is waited for by the
+    first access to one of its tensors; shard_locally works through the files in order."""
+    case = [c for c in cases.CASES if c["id"] == "llama3_70b_w8"][0]       # 30 files
+    paths = case_files(case)
+    world = case["world"]
+    plan = OrderedDict(cases.plan(case))
+    loader = fst.SafeTensorsFileLoader(fst.SingleGroup(), "cpu", nogds=True, max_threads=2, slot_kb=64)
+    loader.add_filenames({0: paths})
+    fb = loader.copy_files_to_device(wait=False)
+    factories = fb.rank_loaders[0]
+    assert all(f.pending for f in factories)
+    per_rank = fb.shard_locally(plan, world)
+    assert not any(f.pending for f in factories)
+    for rank, tensors in enumerate(per_rank):
+        want = {k: v for k, v in golden["cases"][case["id"]][rank].items() if v is not None}
+        assert {k: record(v) for k, v in tensors.items()} == want
+    fb.close()
+    # per-tensor access completes just the file it touches; close() drains what is still pending
+    loader.reset()
+    loader.add_filenames({0: paths})
+    fb = loader.copy_files_to_device(wait=False)
+    name = next(iter(fb.rank_loaders[0][3].metadata.tensors))
+    fo = st_oracle.FileOracle(fb.rank_loaders[0][3].metadata.src)
+    assert digest_bytes(tensor_bytes(fb.get_tensor(name))) == digest_bytes(fo.raw(name))
+    assert not fb.rank_loaders[0][3].pending and fb.rank_loaders[0][4].pending
+    fb.close()
+    loader.close()
+
+
+def test_deferred_wait_reports_a_failed_read_at_first_access(case_files, leak_check):
+    import errno
+
+    case = [c for c in cases.CASES if c["id"] == "llama3_8b_w8"][0]
+    paths = case_files(case)
+    loader = fst.SafeTensorsFileLoader(fst.SingleGroup(), "cpu", nogds=True, max_threads=1, slot_kb=4)
+    loader.add_filenames({0: paths})
+    loader.copier_constructor.reader.inject_fault(3, errno.EIO)
+    fb = loader.copy_files_to_device(wait=False)           # nothing is raised here
+    with pytest.raises(Exception, match="failed"):
+        for name in fb.key_to_rank_lidx:
+            fb.get_tensor(name)
+    fb.close()
+    loader.close()
+
+
 def test_fix_alignment_pads_the_header_only(case_files, tmp_path, leak_check):
     from fastsafetensors_b200.fix_alignment import aligned_copy
 

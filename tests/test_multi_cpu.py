@@ -34,7 +34,8 @@ def _rank_main(rank, world, case, paths, port, out_dir, batched=False, backend="
         device = "cpu"
     loader = fst.SafeTensorsFileLoader(dist.group.WORLD, device, nogds=True, max_threads=2, slot_kb=64)
     loader.add_filenames(cases.owners(paths, world))
-    fb = loader.copy_files_to_device()
+    # the batched run also defers the waits: files are waited for chunk by chunk inside exchange
+    fb = loader.copy_files_to_device(wait=not batched)
     out = {}
     for step in case["steps"]:
         if step[0] == "plan" and batched:

@@ -452,6 +452,8 @@ def b200_arm(args) -> dict:
     parity["what"] = "SHA-256 of result bytes (device -> host) against regenerated tensor data, after the timed steps"
     # a light device -> host read of the result
     check = int(ex.recv[:: max(1, ex.recv.numel() // 4096)].to(torch.int64).sum().item())
+    if isinstance(ex, PeerShardExchange):
+        ex.close()          # collective: the ranks unmap each other's arenas
     del ex
     fb.close()
     loader.close()

@@ -381,18 +381,18 @@ class PeerArenaUnavailable(RuntimeError):
 
 
 class PeerArena:
-    """This rank's receive arena (plain ``cudaMalloc``, exported over CUDA IPC) and the mappings
-    of every peer's arena.  Creating one is a collective (the handles are all-gathered), and
-    mapping a peer's arena costs tens of milliseconds per peer, so arenas are kept per process
-    group (``PeerArena.for_group``) and reused by later exchanges; what a rank receives is copied
-    out of the arena into its own tensor memory.
+    """This rank's receive arena for one exchange (plain ``cudaMalloc``, exported over CUDA IPC)
+    and the mappings of every peer's arena.  What a rank receives stays in its arena: the result
+    tensors are views of it and keep it alive, so nothing is copied out.
 
-    A failure on one rank must not leave the others waiting in a collective, so the constructor
-    never raises between its collectives: each rank carries its own error through the two
-    all-gathers (handles, then the outcome of mapping them), all ranks undo what they did, and all
-    raise ``PeerArenaUnavailable`` together."""
+    Creating one is a collective (the handles are all-gathered).  A failure on one rank must not
+    leave the others waiting in a collective, so the constructor never raises between its
+    collectives: each rank carries its own error through the two all-gathers (handles, then the
+    outcome of mapping them), all ranks undo what they did, and all raise
+    ``PeerArenaUnavailable`` together.  ``close_peers`` (collective) unmaps the peers once the
+    exchange is over; from then on every arena belongs to its own rank alone and is freed when
+    the last tensor over it is gone."""
 
-    _cache: Dict[Tuple[int, str], "PeerArena"] = {}
     _failed: Dict[Tuple[int, str], str] = {}
 
     def __init__(self, pg, nbytes: int, device):
@@ -411,6 +411,7 @@ class PeerArena:
         self.address = 0
         self.peer_base: List[int] = []
         self._alive = False
+        self._shared = False          # peers may still have this rank's arena mapped
         err: Optional[str] = None
         handle = ctypes.create_string_buffer(nat.ARENA_HANDLE_BYTES)
         try:
@@ -447,159 +448,215 @@ class PeerArena:
             self._undo()
             raise PeerArenaUnavailable("peer arenas cannot be set up: " + "; ".join(problems))
         self._alive = True
+        self._shared = True
+
+    def _unmap_peers(self) -> None:
+        for r, p in enumerate(self.peer_base):
+            if r != self.rank and p:
+                self._nat.lib.fst_arena_close_peer(p)
+        self.peer_base = []
 
     def _undo(self) -> None:
         """Unmap what this rank mapped, wait until every rank has, free this rank's arena."""
         import torch.distributed as dist
 
-        for r, p in enumerate(self.peer_base):
-            if r != self.rank and p:
-                self._nat.lib.fst_arena_close_peer(p)
-        self.peer_base = []
+        self._unmap_peers()
         dist.barrier(group=self.pg.real_pg)
+        self._shared = False
+        self._free()
+
+    def _free(self) -> None:
         if self.address:
             self._nat.lib.fst_arena_destroy(self.address)
             self.address = 0
 
     @classmethod
     def for_group(cls, pg, nbytes: int, device) -> "PeerArena":
-        """The group's arena, grown if needed.  ``nbytes`` must be the same on every rank (callers
-        pass the largest need of any rank), so that all ranks decide alike whether to grow.
-        A group whose arenas could not be set up once is not tried again."""
+        """A new arena of ``nbytes`` on every rank of the group (collective; ``nbytes`` must be
+        the same on every rank).  A group whose arenas could not be set up once is not tried
+        again: the failure is remembered and raised at once, without a collective."""
         key = (id(pg.real_pg), device.as_str())
         if key in cls._failed:
             raise PeerArenaUnavailable(cls._failed[key])
-        cur = cls._cache.get(key)
-        if cur is not None and cur.nbytes >= nbytes:
-            return cur
-        if cur is not None:
-            cur.destroy()
-            del cls._cache[key]
-        grown = max(int(nbytes * 1.25), 64 << 20)
         try:
-            cls._cache[key] = cls(pg, (grown + (1 << 21) - 1) >> 21 << 21, device)
+            return cls(pg, (int(nbytes) + (1 << 21) - 1) >> 21 << 21, device)
         except PeerArenaUnavailable as e:
             cls._failed[key] = str(e)
             raise
-        return cls._cache[key]
 
     @classmethod
     def known_unusable(cls, pg, device) -> bool:
         """True once setting up arenas for this group has failed (on every rank alike)."""
         return (id(pg.real_pg), device.as_str()) in cls._failed
 
-    @classmethod
-    def release_all(cls) -> None:
-        """Destroy every cached arena.  Collective per process group (each ends in a barrier)."""
-        for arena in list(cls._cache.values()):
-            arena.destroy()
-        cls._cache.clear()
+    def close_peers(self) -> None:
+        """Collective: the work queued so far is drained, every rank unmaps its peers, and all
+        meet in a barrier.  After it nobody but the owner can touch an arena."""
+        import torch
+        import torch.distributed as dist
+
+        if not self._alive or not self._shared:
+            return
+        torch.cuda.synchronize()
+        self._unmap_peers()
+        dist.barrier(group=self.pg.real_pg)
+        self._shared = False
 
     def destroy(self) -> None:
-        """Unmap the peers, wait for every rank to have done so, then free this rank's arena."""
-        import torch
-
+        """Collective unless ``close_peers`` has run: unmap, meet, free this rank's arena."""
         if not self._alive:
             return
+        self.close_peers()
         self._alive = False
-        torch.cuda.synchronize()
-        self._undo()
+        self._free()
+
+    def __del__(self) -> None:
+        # the last tensor over the arena is gone.  If the peers were never told to unmap it
+        # (an exchange abandoned half-way), the memory is left to the process's teardown.
+        try:
+            if self._alive and not self._shared:
+                self._alive = False
+                self._free()
+        except Exception:  # noqa: BLE001
+            pass
 
     def view(self, nbytes: int):
-        """Non-owning ``torch.uint8`` view of the first ``nbytes`` of this rank's arena."""
+        """``torch.uint8`` tensor over the first ``nbytes`` of this rank's arena.  The tensor
+        (and every view derived from it) keeps the arena object alive."""
         import torch
 
-        class _Span:
-            __cuda_array_interface__ = {
-                "shape": (max(int(nbytes), 1),), "typestr": "|u1", "data": (self.address, False), "version": 2,
-            }
-
-        return torch.as_tensor(_Span(), device=self.device.as_str())[: int(nbytes)]
+        return torch.as_tensor(_ArenaSpan(self, nbytes), device=self.device.as_str())[: int(nbytes)]
 
 
-class PeerShardExchange(ShardExchange):
-    """``ShardExchange`` whose transport is the gather kernel itself.
+class _ArenaSpan:
+    """What ``torch.as_tensor`` wraps: the arena's bytes through the CUDA array interface.  torch
+    keeps this object for as long as the storage lives, and the object keeps the arena."""
 
-    Every rank has a peer arena (see ``PeerArena``) that the other ranks have mapped.  The
-    owner's single gather launch stores each shard directly where it is needed: its own region
-    into its receive buffer, every other region into the arena of the destination rank, over
-    NVLink, with ordinary 16-byte stores.  No send buffer and no ``all_to_all``.  One step is
+    def __init__(self, arena: "PeerArena", nbytes: int):
+        self.owner = arena
+        self.__cuda_array_interface__ = {
+            "shape": (max(int(nbytes), 1),), "typestr": "|u1", "data": (arena.address, False), "version": 2,
+        }
 
-        barrier (all ranks have emptied their arenas) -> gather launch -> barrier (all ranks'
-        kernels are complete) -> copy of what arrived from the arena into this rank's own buffer
 
-    where a barrier is an 8-byte all-reduce on the same stream, so nothing synchronises the host.
+class PeerShardExchange:
+    """The exchange with the gather kernel itself as transport.
+
+    Every rank has a peer arena (see ``PeerArena``) sized for everything it will receive, which
+    the other ranks have mapped.  The requests are cut into chunks round by round, as in
+    ``ShardExchange``; per chunk the owner's ONE gather launch stores each shard directly where
+    it is needed: its own region into its own arena, every other region into the arena of the
+    destination rank, over NVLink, with ordinary 16-byte stores.  No send buffer, no
+    ``all_to_all``, no copy out of the arena: the results are views of it.  After the last
+    chunk one 4-byte all-reduce on the same stream tells every rank that all kernels (and with
+    them all peer stores) are complete; nothing synchronises the host.  With deferred reads
+    (``copy_files_to_device(wait=False)``) the launches of round k run while the reader fills the
+    files of round k+1.
+
+    Regions are disjoint per (owner, destination) pair, so ``run()`` may be repeated.
     """
 
-    def __init__(self, fb, requests: "Dict[str, Action]", world: int, me: int):
+    def __init__(self, fb, requests: "Dict[str, Action]", world: int, me: int,
+                 chunk_bytes: Optional[int] = None):
         import torch
-
-        from . import _native as nat
 
         self.fb, self.world, self.me, self.local = fb, world, me, False
         self.names = list(requests)
-        self.layout = BatchLayout(world)
-        self.frames = {}
-        src_addr: Dict[str, int] = {}
+        self.frames: Dict[str, TensorFrame] = {}
         self.device = next(l.device for ls in fb.rank_loaders.values() for l in ls)
         if self.device.is_cpu:
             raise Exception("the peer transport needs CUDA devices")
-        for name in self.names:
-            rank, lidx = fb._get_rank_lidx(name)
-            loader = fb.rank_loaders[rank][lidx]
-            self.frames[name] = loader.metadata.tensors[name]
-            self.layout.add(name, self.frames[name], rank, requests[name])
-            if rank == me:
-                if name not in loader.tensors:
-                    raise Exception(f"exchange: tensor {name} was not found, released? lidx={loader.lidx}")
-                src_addr[name] = loader.tensors[name].data_ptr()
-        lay = self.layout
-        # the arena holds what the OTHER ranks send; every rank sizes it for the neediest rank
-        need = max(sum(lay.recv_sizes(r)) for r in range(world))
-        self.arena = PeerArena.for_group(fb.pg, need, self.device)
-        self.incoming = sum(lay.recv_sizes(me))
-        self.recv = torch.empty(lay.recv_total(me), dtype=torch.uint8, device=self.device.as_str())
+        self.chunks: List[_Chunk] = []
+        self.chunk_base: List[List[int]] = []      # [chunk][rank] -> offset in that rank's arena
+        total = [0] * world
+        for names in cut_into_chunks(fb, requests, world, chunk_bytes or (1 << 62)):
+            lay = BatchLayout(world)
+            for name in names:
+                rank, lidx = fb._get_rank_lidx(name)
+                frame = fb.rank_loaders[rank][lidx].metadata.tensors[name]
+                self.frames[name] = frame
+                lay.add(name, frame, rank, requests[name])
+            self.chunk_base.append(list(total))
+            self.chunks.append(_Chunk(names, lay, total[me], lay.recv_total(me), 0))
+            for r in range(world):
+                total[r] += lay.recv_total(r)
+        # every rank allocates for the neediest rank, so that all decide alike
+        self.arena = PeerArena.for_group(fb.pg, max(total), self.device)
+        self.recv = self.arena.view(total[me])
         self.send = None
-        self._arena_view = self.arena.view(self.incoming)
-        # region [me -> d]: d's arena at the offset where d expects owner `me`; own region: recv
-        region = [self.arena.peer_base[d] + lay.recv_offset(d, me) for d in range(world)]
-        region[me] = self.recv.data_ptr() + lay.recv_offset(me, me)
-        mine = {n: f for n, f in self.frames.items() if n in src_addr}
-        ops = lay.fill_ops(me, mine, src_addr, region, rotate=True) if mine else []
-        self.payload_bytes = sum(o[2] * o[3] for o in ops)
-        self.egress_bytes = sum(lay.region_bytes[me][d] for d in range(world) if d != me)
-        self.launches = [(nat.pack_ops(ops), len(ops))] if ops else []
+        self.payload_bytes = 0
+        self.egress_bytes = sum(ch.layout.region_bytes[me][d] for ch in self.chunks
+                                for d in range(world) if d != me)
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device.as_str())
 
-    def _launch_gathers(self, timing: Optional[list]) -> None:
+    def _prepare(self, index: int) -> _Chunk:
+        ch = self.chunks[index]
+        if ch.launches is not None:
+            return ch
+        from . import _native as nat
+
+        fb, lay, me = self.fb, ch.layout, self.me
+        src_addr: Dict[str, int] = {}
+        for name in ch.names:
+            rank, lidx = fb._get_rank_lidx(name)
+            if rank == me:
+                loader = fb.rank_loaders[rank][lidx]
+                tensors = loader.tensors          # completes a deferred read of the file
+                if name not in tensors:
+                    raise Exception(f"exchange: tensor {name} was not found, released? lidx={loader.lidx}")
+                src_addr[name] = tensors[name].data_ptr()
+        # region [me -> d]: d's arena, this chunk's part, at the offset where d expects owner `me`
+        base = self.chunk_base[index]
+        region = [self.arena.peer_base[d] + base[d] + lay.recv_offset(d, me) for d in range(self.world)]
+        mine = {n: self.frames[n] for n in src_addr}
+        ops = lay.fill_ops(me, mine, src_addr, region, rotate=True) if mine else []
+        ch.payload = sum(o[2] * o[3] for o in ops)
+        ch.launches = [(nat.pack_ops(ops), len(ops))] if ops else []
+        return ch
+
+    def run(self, timing: Optional[list] = None, after_chunk=None) -> None:
         import torch
+        import torch.distributed as dist
 
         from . import _native as nat
 
         stream = self.fb.framework.current_stream(self.device)
-        for packed, n in self.launches:
-            if timing is not None:
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-            nat.check(nat.lib.fst_gather(packed.pointer, n, 0, 0, 0, 0, stream), "fst_gather")
-            if timing is not None:
-                b.record()
-                timing.append((a, b))
+        payload = 0
+        for index in range(len(self.chunks)):
+            ch = self._prepare(index)
+            payload += ch.payload
+            for packed, n in ch.launches:
+                if timing is not None:
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                nat.check(nat.lib.fst_gather(packed.pointer, n, 0, 0, 0, 0, stream), "fst_gather")
+                if timing is not None:
+                    b.record()
+                    timing.append((a, b))
+            if after_chunk is not None:
+                after_chunk(ch.names)
+        self.payload_bytes = payload
+        # every rank's kernels are complete (a kernel's peer stores are visible when it completes)
+        dist.all_reduce(self._flag, group=self.fb.pg.real_pg)
+
+    def _view(self, slot: Slot, off: int):
+        from .frameworks._torch import TorchTensor, dtype_convert
+
+        frame = self.frames[slot.name]
+        native = self.fb.framework.get_native_shape(frame.dtype, slot.shape)
+        t = self.recv[off: off + slot.nbytes].view(dtype_convert[frame.dtype]).reshape(native)
+        return TorchTensor(self.device, frame.dtype, t)
 
     def results(self):
-        return {slot.name: self._view(slot, off) for slot, off in self.layout.received(self.me)}
+        out = {}
+        for ch in self.chunks:
+            for slot, off in ch.layout.received(self.me):
+                out[slot.name] = self._view(slot, ch.recv_base + off)
+        return out
 
-    def run(self, timing: Optional[list] = None, after_chunk=None) -> None:
-        import torch.distributed as dist
-
-        group = self.fb.pg.real_pg
-        dist.all_reduce(self._flag, group=group)      # every rank has emptied its arena
-        self._launch_gathers(timing)
-        dist.all_reduce(self._flag, group=group)      # every rank's kernel is complete
-        if self.incoming:
-            self.recv[: self.incoming].copy_(self._arena_view)
-        if after_chunk is not None:
-            after_chunk(self.names)
+    def close(self) -> None:
+        """Collective: the peers let go of each other's arenas (the results stay valid)."""
+        self.arena.close_peers()
 
     def finish(self) -> None:
-        """Kept for callers of the earlier interface; the arena now outlives the exchange."""
+        self.close()

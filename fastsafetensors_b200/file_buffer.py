@@ -186,11 +186,11 @@ class FilesBufferOnDevice:
 
         ``transport``: ``"nccl"`` packs into a send buffer and exchanges with
         ``all_to_all_single``; ``"peer"`` (CUDA devices of one machine) lets the gather kernel
-        store every shard straight into the destination rank's receive arena over NVLink, and
-        raises ``PeerArenaUnavailable`` on every rank if the ranks cannot map each other's
-        memory; ``"auto"`` uses ``"peer"`` where it measured faster than the collective (two
-        ranks: 7.4 ms against 9.5 ms for a 16 GB checkpoint; equal at four) and falls back to
-        ``"nccl"``, on all ranks together, where peer mapping is refused.
+        store every shard straight into the destination rank's receive arena over NVLink (the
+        results are views of that arena), and raises ``PeerArenaUnavailable`` on every rank if
+        the ranks cannot map each other's memory; ``"auto"`` uses ``"peer"`` for groups of up to
+        ``PEER_AUTO_MAX_WORLD`` ranks and falls back to ``"nccl"``, on all ranks together, where
+        peer mapping is refused.
         Default: the ``FST_B200_TRANSPORT`` environment variable, else ``"auto"``.
         """
         from .batch import PeerArena, PeerArenaUnavailable, PeerShardExchange, ShardExchange, default_chunk_bytes
@@ -213,42 +213,24 @@ class FilesBufferOnDevice:
                 self._mark(*self.key_to_rank_lidx[name], name)
 
         if transport in ("peer", "auto"):
-            done: List[str] = []
             try:
-                for names in self._batches(requests, world, max_batch_bytes):
-                    batch = OrderedDict((n, requests[n]) for n in names)
-                    ex = PeerShardExchange(self, batch, world, me)
-                    ex.run(after_chunk=release)
-                    out.update(ex.results())
-                    done += names
-                return out
+                ex = PeerShardExchange(self, requests, world, me,
+                                       chunk_bytes=max_batch_bytes if max_batch_bytes < (8 << 30) else None)
             except PeerArenaUnavailable as e:
                 # raised by all ranks at the same call, so all take the same branch
                 if not fall_back:
                     raise
                 logger.warning("exchange: %s; using the NCCL all-to-all", e)
-                requests = OrderedDict((n, a) for n, a in requests.items() if n not in set(done))
+            else:
+                ex.run(after_chunk=release)
+                out.update(ex.results())
+                ex.close()
+                return out
         ex = ShardExchange(self, requests, world, me, local=False,
                            chunk_bytes=min(max_batch_bytes, default_chunk_bytes()))
         ex.run(after_chunk=release)
         out.update(ex.results())
         return out
-
-    def _batches(self, requests, world: int, max_batch_bytes: int) -> List[List[str]]:
-        """Cut requests (in order) so that no owner sends more than ``max_batch_bytes`` a batch."""
-        batches: List[List[str]] = [[]]
-        volume = [0] * world
-        for name, action in requests.items():
-            rank, lidx = self._get_rank_lidx(name)
-            frame = self.rank_loaders[rank][lidx].metadata.tensors[name]
-            nbytes = frame.data_offsets[1] - frame.data_offsets[0]
-            cost = nbytes * (world if action[0] == "replicate" else 1)
-            if batches[-1] and volume[rank] + cost > max_batch_bytes:
-                batches.append([])
-                volume = [0] * world
-            batches[-1].append(name)
-            volume[rank] += cost
-        return [b for b in batches if b]
 
     def shard_locally(self, requests: "OrderedDict[str, Tuple]", world_size: int) -> List[Dict[str, TensorBase]]:
         """Single-process form of ``exchange``: this process (which must own every file of the

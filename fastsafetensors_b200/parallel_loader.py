@@ -1,14 +1,23 @@
-"""Pipelined loading: a producer thread reads batch k+1 of files while the caller consumes the
-tensors of batch k.
+"""Pipelined loading: batch k+1 of files is read while the caller consumes the tensors of
+batch k.
 
 Same classes, arguments and iteration contract as upstream ``fastsafetensors/parallel_loader.py``
 (``PipelineParallel``, ``ParallelLoader``, ``iterate_weights`` yielding ``(key, tensor)`` in
 ``key_to_rank_lidx`` order, batches of ``world_size`` files with file ``i`` of a batch owned by
-rank ``i``; ``queue_size`` -1 / 0 / N as upstream defines them).  What differs with more than one
-rank: upstream broadcasts every tensor on its own (``parallel_loader.py:337-350`` ->
-``tensor_factory.py:128-143``, a collective and a device synchronisation per tensor); here each
-FILE image is broadcast once (``FilesBufferOnDevice.replicate_all``) and the tensors are views of
-the received images, so a batch costs ``world_size`` collectives instead of one per tensor.
+rank ``i``; ``queue_size`` -1 / 0 / N as upstream defines them).  Two things differ.
+
+* Where the overlap lives.  Upstream runs ``copy_files_to_device`` of the next batch on a Python
+  producer thread and hands batches over through a queue (``parallel_loader.py:284-308``).  Here
+  the native reader is the producer: the reads of the batches ahead are *queued* with
+  ``copy_files_to_device(wait=False)`` (double- or N-buffered file images, filled by the reader's
+  worker threads through its pinned ring) and each file is waited for when its first tensor is
+  taken.  No Python thread, no hand-over between threads.  ``producer_thread=True`` (or
+  ``FST_B200_PIPELINE_THREAD=1``) selects upstream's arrangement instead.
+* With more than one rank upstream broadcasts every tensor on its own
+  (``parallel_loader.py:337-350`` -> ``tensor_factory.py:128-143``, a collective and a device
+  synchronisation per tensor); here each FILE image is broadcast once
+  (``FilesBufferOnDevice.replicate_all``) and the tensors are views of the received images, so a
+  batch costs ``world_size`` collectives instead of one per tensor.
 """
 
 from __future__ import annotations
@@ -87,7 +96,7 @@ class PipelineParallel:
 
     def __init__(self, pg: Optional[Any], loader: BaseSafeTensorsFileLoader, hf_weights_files: List[str],
                  max_concurrent_producers: int = 1, queue_size: int = 0, use_tqdm_on_load: bool = True,
-                 **kwargs):
+                 producer_thread: Optional[bool] = None, **kwargs):
         if max_concurrent_producers != 1:
             raise ValueError(
                 f"max_concurrent_producers must be 1 (got {max_concurrent_producers}). "
@@ -116,6 +125,9 @@ class PipelineParallel:
         self.print_log = os.getenv("FASTSAFETENSORS_DEBUG", "false").lower() == "true"
         self.log_prefix = f"PG{self.pg.rank()}"
         self.need_clone = world == 1
+        if producer_thread is None:
+            producer_thread = os.getenv("FST_B200_PIPELINE_THREAD", "0") == "1"
+        self.producer_thread = bool(producer_thread)
         fstcpp.set_gil_release(True)
 
     # ------------------------------------------------------------------ logging
@@ -126,15 +138,15 @@ class PipelineParallel:
             print(f"[{self.log_prefix}] {stamp} - {message}", flush=True)
 
     # ------------------------------------------------------------------ producer
-    def _load_batch(self, batch_id: int, files: List[str]) -> Optional[FileBatch]:
+    def _load_batch(self, batch_id: int, files: List[str], wait: bool = True) -> Optional[FileBatch]:
         with TimingContext("add_filenames", self._log_message, batch_id) as t_add:
             self.loader.add_filenames({i: [f] for i, f in enumerate(files)})
-        if self._ticket is not None:
+        if wait and self._ticket is not None:
             while not self._ticket.acquire(timeout=0.2):
                 if self.stop_event.is_set():
                     return None
         with TimingContext("copy_files_to_device", self._log_message, batch_id) as t_copy:
-            fb = self.loader.copy_files_to_device()
+            fb = self.loader.copy_files_to_device() if wait else self.loader.copy_files_to_device(wait=False)
         batch = FileBatch(fb, list(fb.key_to_rank_lidx.keys()), batch_id)
         batch.add_filenames_time, batch.copy_files_time = t_add.elapsed_ms, t_copy.elapsed_ms
         batch.load_time = t_add.elapsed_ms + t_copy.elapsed_ms
@@ -182,7 +194,7 @@ class PipelineParallel:
         finally:
             with TimingContext("fb.close", self._log_message, batch.batch_id) as t_close:
                 batch.fb.close()
-            if self._ticket is not None and self.queue_size < 0:
+            if self.producer_thread and self._ticket is not None and self.queue_size < 0:
                 self._ticket.release()
         self._log_message(
             f"Batch {batch.batch_id} summary: add_filenames={batch.add_filenames_time:.3f}ms, "
@@ -191,6 +203,62 @@ class PipelineParallel:
 
     def iterate_weights(self) -> Generator[Tuple[str, Any], None, None]:
         """Yield ``(key, tensor)`` for every tensor of every file, batch by batch."""
+        if self.producer_thread:
+            yield from self._iterate_with_producer_thread()
+        else:
+            yield from self._iterate_native()
+
+    def _iterate_native(self) -> Generator[Tuple[str, Any], None, None]:
+        """The native reader as producer.  ``ahead`` batches beyond the one being consumed have
+        their reads queued: none for ``queue_size`` -1 (the next batch starts when this one is
+        closed), one for 0, ``queue_size + 1`` for N > 0 -- the same number of file images in
+        device memory as upstream's queue holds.  A failure to queue a batch (a missing file,
+        say) is kept and raised when the consumer reaches that batch, as upstream's queue
+        delivers the producer's exception in order."""
+        ahead = 0 if self.queue_size < 0 else self.queue_size + 1
+        batches = self.weight_files_batches
+        queued: "List[Union[FileBatch, Exception]]" = []
+        next_id = 0
+        bar = tqdm(total=len(batches), desc="Loading fastsafetensors checkpoint shards",
+                   disable=not enable_tqdm(self.use_tqdm_on_load, self.loader.framework),
+                   bar_format=_BAR_FORMAT) if _TQDM_AVAILABLE else None
+
+        def top_up(target: int) -> None:
+            nonlocal next_id
+            while len(queued) < target and next_id < len(batches):
+                if queued and isinstance(queued[-1], Exception):
+                    return                     # nothing is queued behind a failed batch
+                try:
+                    item = self._load_batch(next_id, batches[next_id], wait=False)
+                except Exception as e:  # noqa: BLE001
+                    self.error_info = f"Producer failed: {e}"
+                    self.error_event.set()
+                    item = e
+                    self.loader.reset()
+                queued.append(item)
+                next_id += 1
+
+        try:
+            top_up(1)
+            while queued:
+                item = queued.pop(0)
+                if isinstance(item, Exception):
+                    raise item
+                top_up(ahead)                  # reads of the batches ahead run while this one is consumed
+                yield from self._consume_batch(item)
+                if bar is not None:
+                    bar.update(1)
+                top_up(1)
+        finally:
+            self.stop_event.set()
+            if bar is not None:
+                bar.close()
+            for left in queued:               # batches that were queued but never consumed
+                if isinstance(left, FileBatch):
+                    left.fb.close()
+
+    def _iterate_with_producer_thread(self) -> Generator[Tuple[str, Any], None, None]:
+        """Upstream's arrangement: a Python producer thread and a queue of loaded batches."""
         producer = threading.Thread(target=self._producer_worker, name="fst-producer", daemon=True)
         producer.start()
         bar = tqdm(total=len(self.weight_files_batches), desc="Loading fastsafetensors checkpoint shards",
@@ -242,9 +310,10 @@ class ParallelLoader(PipelineParallel):
     def __init__(self, pg: Optional[Any], hf_weights_files: List[str], max_concurrent_producers: int = 1,
                  queue_size: int = 0, use_tqdm_on_load: bool = True, device: Any = "cpu",
                  bbuf_size_kb: int = 16 * 1024, max_threads: int = 16, nogds: bool = False,
-                 set_numa: bool = True, debug_log: bool = False, framework="pytorch", **kwargs):
+                 set_numa: bool = True, debug_log: bool = False, framework="pytorch",
+                 producer_thread: Optional[bool] = None, **kwargs):
         loader = SafeTensorsFileLoader(pg, device, bbuf_size_kb=bbuf_size_kb, max_threads=max_threads,
                                        nogds=nogds, disable_cache=True, set_numa=set_numa,
                                        debug_log=debug_log, framework=framework, **kwargs)
         super().__init__(pg, loader, hf_weights_files, max_concurrent_producers, queue_size,
-                         use_tqdm_on_load)
+                         use_tqdm_on_load, producer_thread=producer_thread)

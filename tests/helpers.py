@@ -35,3 +35,11 @@ def free_port() -> int:
     with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
         sock.bind(("127.0.0.1", 0))
         return sock.getsockname()[1]
+
+
+def rendezvous(out_dir: str, token) -> str:
+    """``init_method`` for a test's process group: a file in the test's own directory.  No TCP
+    port is involved, so two tests (or two test runs on one machine) cannot collide on one."""
+    import os
+
+    return "file://" + os.path.join(str(out_dir), f"rendezvous_{token}")

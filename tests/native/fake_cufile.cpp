@@ -1,8 +1,8 @@
 // A host-side double of the seven cuFile entry points libfst_b200.so resolves, for tests.
 //
 // It never touches NVIDIA's libcufile, the cuFile driver or the nvidia-fs module: a "cuFileRead"
-// is a pread into host memory followed by a synchronous cudaMemcpy to devPtr_base +
-// devPtr_offset.  That is enough to run the reader's cuFile code path (driver reference count,
+// is a pread into host memory followed by a copy to devPtr_base + devPtr_offset that is complete
+// when the call returns.  That is enough to run the reader's cuFile code path (driver reference count,
 // register-once staging ring, per-request file handles, 4096-aligned windows into staging slots,
 // realign kernel to the destination) on any machine with a CUDA device.  The marker symbol
 // `fst_cufile_stand_in` tells the reader that this library needs no nvidia-fs.
@@ -141,8 +141,17 @@ __attribute__((visibility("default"))) ssize_t cuFileRead(CUfileHandle_t fh, voi
         got += (size_t)c;
         if (got % 4096) break;  // a ragged count under O_DIRECT means end of file
     }
-    const bool ok = got == 0 || cudaMemcpy((unsigned char *)devPtr_base + devPtr_offset, host, got,
-                                           cudaMemcpyHostToDevice) == cudaSuccess;
+    // cuFileRead returns when the bytes ARE in device memory.  A plain cudaMemcpy from pageable
+    // memory may return while its DMA is still in flight, so the copy goes through a stream of
+    // this thread's own and waits for it.
+    static thread_local cudaStream_t stream = nullptr;
+    bool ok = true;
+    if (got) {
+        if (stream == nullptr) ok = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) == cudaSuccess;
+        ok = ok && cudaMemcpyAsync((unsigned char *)devPtr_base + devPtr_offset, host, got,
+                                   cudaMemcpyHostToDevice, stream) == cudaSuccess;
+        ok = ok && cudaStreamSynchronize(stream) == cudaSuccess;
+    }
     std::free(host);
     if (!ok) return -1;
     g_read_bytes += (int64_t)got;

@@ -12,7 +12,7 @@ from safetensors.torch import load_file, save_file
 
 import fastsafetensors_b200 as fst
 from oracle import st_oracle
-from tests.helpers import free_port
+from tests.helpers import free_port, rendezvous
 
 
 def _empty_mix(path: str) -> dict:
@@ -103,14 +103,14 @@ def _two_rank_main(rank, world, path, port, out_dir, backend):
 
     import torch.distributed as dist
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    rdzv = rendezvous(out_dir, port)
     if backend == "nccl":
         torch.cuda.set_device(rank)
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+        dist.init_process_group("nccl", init_method=rdzv, rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
         device = f"cuda:{rank}"
     else:
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        dist.init_process_group("gloo", init_method=rdzv, rank=rank, world_size=world)
         device = "cpu"
     fo = st_oracle.FileOracle(path)
     plan = OrderedDict([("e2", ("shard", 1)), ("mid0", ("shard", 1)), ("x", ("shard", 1)),

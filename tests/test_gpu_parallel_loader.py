@@ -1,7 +1,9 @@
 """PipelineParallel / ParallelLoader on a CUDA device (upstream parallel_loader.py:284-308,
-364-412): the producer thread runs ``add_filenames`` / ``copy_files_to_device`` / ``reset`` for
-batch k+1 while the consumer thread takes tensors of batch k and closes it -- native submit and
-wait from one thread, tensor instantiation and image release from another."""
+364-412), in both arrangements: the native reader as producer (reads of the batches ahead queued
+without waiting, files waited for at first use), and upstream's producer thread (``add_filenames``
+/ ``copy_files_to_device`` / ``reset`` for batch k+1 on one thread while another takes tensors of
+batch k and closes it -- native submit and wait from one thread, tensor instantiation and image
+release from another)."""
 
 import threading
 
@@ -27,12 +29,13 @@ def _expected(paths):
     return want
 
 
+@pytest.mark.parametrize("producer_thread", [False, True], ids=["native_read_ahead", "producer_thread"])
 @pytest.mark.parametrize("queue_size", [-1, 0, 2])
-def test_pipeline_on_cuda_yields_every_tensor_once(queue_size, case_files, leak_check):
+def test_pipeline_on_cuda_yields_every_tensor_once(queue_size, producer_thread, case_files, leak_check):
     paths = sorted(case_files(CASE))
     want = _expected(paths)
     it = fst.ParallelLoader(None, paths, queue_size=queue_size, use_tqdm_on_load=False, device=DEV,
-                            nogds=True, max_threads=4, slot_kb=64)
+                            nogds=True, max_threads=4, slot_kb=64, producer_thread=producer_thread)
     got, consumer = {}, threading.get_ident()
     producers = set()
     real_copy = it.loader.copy_files_to_device
@@ -49,7 +52,10 @@ def test_pipeline_on_cuda_yields_every_tensor_once(queue_size, case_files, leak_
         got[key] = (list(t.shape), digest_tensor(t))
     it.close()
     assert got == want
-    assert producers and consumer not in producers      # the copies ran on the producer thread
+    if producer_thread:
+        assert producers and consumer not in producers      # the copies ran on the producer thread
+    else:
+        assert producers == {consumer}                      # queued from the consumer, read natively
     # tensors kept past the end of their batch still hold their own bytes
     torch.cuda.synchronize()
     for (key, (_, d)), t in zip(got.items(), keep):

@@ -12,7 +12,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from tests.golden import cases
-from tests.helpers import free_port
+from tests.helpers import free_port, rendezvous
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -23,14 +23,14 @@ def _rank_main(rank, world, case, paths, port, out_dir, batched=False, backend="
     from fastsafetensors_b200 import cpp
     from tests.helpers import record
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    rdzv = rendezvous(out_dir, port)
     if backend == "nccl":
         torch.cuda.set_device(rank)
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+        dist.init_process_group("nccl", init_method=rdzv, rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
         device = f"cuda:{rank}"
     else:
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        dist.init_process_group("gloo", init_method=rdzv, rank=rank, world_size=world)
         device = "cpu"
     loader = fst.SafeTensorsFileLoader(dist.group.WORLD, device, nogds=True, max_threads=2, slot_kb=64)
     loader.add_filenames(cases.owners(paths, world))
@@ -123,8 +123,8 @@ def _packed_rank(rank, world, path, port, out_dir):
     import fastsafetensors_b200 as fst
     from tests.helpers import digest_tensor
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    rdzv = rendezvous(out_dir, port)
+    dist.init_process_group("gloo", init_method=rdzv, rank=rank, world_size=world)
     loader = fst.SafeTensorsFileLoader(dist.group.WORLD, "cpu", nogds=True, max_threads=2)
     loader.add_filenames({1: [path]})          # owned by rank 1
     fb = loader.copy_files_to_device()
@@ -176,14 +176,14 @@ def _all_keys_rank(rank, world, paths, port, out_dir, backend="gloo"):
     from fastsafetensors_b200 import cpp
     from tests.helpers import digest_tensor
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    rdzv = rendezvous(out_dir, port)
     if backend == "nccl":
         torch.cuda.set_device(rank)
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+        dist.init_process_group("nccl", init_method=rdzv, rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
         device = f"cuda:{rank}"
     else:
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        dist.init_process_group("gloo", init_method=rdzv, rank=rank, world_size=world)
         device = "cpu"
     calls = {"n": 0}
     real = dist.broadcast

@@ -16,7 +16,7 @@ from fastsafetensors_b200.frameworks import get_framework_op
 from oracle import st_oracle
 from tests.golden import cases
 from tests.helpers import digest_bytes, digest_tensor
-from tests.helpers import free_port
+from tests.helpers import free_port, rendezvous
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CASE = [c for c in cases.CASES if c["id"] == "llama3_70b_w8"][0]   # 30 small files
@@ -31,12 +31,13 @@ def _expected(paths):
     return want
 
 
+@pytest.mark.parametrize("producer_thread", [False, True], ids=["native_read_ahead", "producer_thread"])
 @pytest.mark.parametrize("queue_size", [-1, 0, 2])
-def test_single_rank_yields_every_tensor_once(queue_size, case_files, leak_check):
+def test_single_rank_yields_every_tensor_once(queue_size, producer_thread, case_files, leak_check):
     paths = sorted(case_files(CASE))
     want = _expected(paths)
     it = fst.ParallelLoader(None, paths, queue_size=queue_size, use_tqdm_on_load=False, device="cpu",
-                            nogds=True, max_threads=2, slot_kb=64)
+                            nogds=True, max_threads=2, slot_kb=64, producer_thread=producer_thread)
     got = {}
     for key, t in it.iterate_weights():
         assert key not in got
@@ -56,20 +57,51 @@ def test_order_follows_files_then_keys(case_files, leak_check):
     assert keys == want
 
 
-def test_producer_error_reaches_the_consumer(case_files, tmp_path, leak_check):
+@pytest.mark.parametrize("producer_thread", [False, True], ids=["native_read_ahead", "producer_thread"])
+def test_producer_error_reaches_the_consumer(producer_thread, case_files, tmp_path, leak_check):
     paths = sorted(case_files(CASE))[:2] + [str(tmp_path / "missing.safetensors")]
-    it = fst.ParallelLoader(None, paths, use_tqdm_on_load=False, device="cpu", nogds=True)
-    seen = 0
+    it = fst.ParallelLoader(None, paths, use_tqdm_on_load=False, device="cpu", nogds=True, queue_size=2,
+                            producer_thread=producer_thread)
+    seen = set()
     with pytest.raises(Exception):
-        for _ in it.iterate_weights():
-            seen += 1
+        for key, _ in it.iterate_weights():
+            seen.add(key)
     it.close()
-    assert seen > 0
+    # the failure is delivered in order: every tensor of the two good files came first
+    want = set()
+    for p in paths[:2]:
+        want |= set(st_oracle.FileOracle(p).tensors)
+    assert seen == want
 
 
-def test_consumer_may_stop_early(case_files, leak_check):
+def test_read_ahead_depth_follows_queue_size(case_files, leak_check):
+    """How many batches have their reads queued beyond the one being consumed: none for -1, one
+    for 0, queue_size + 1 for N > 0 (the images upstream's queue and producer hold)."""
+    paths = sorted(case_files(CASE))[:8]
+    for queue_size, ahead in ((-1, 0), (0, 1), (2, 3)):
+        it = fst.ParallelLoader(None, paths, queue_size=queue_size, use_tqdm_on_load=False, device="cpu",
+                                nogds=True, max_threads=2, slot_kb=64)
+        real = it.loader.copy_files_to_device
+        submitted = []
+
+        def spy(*a, _real=real, **kw):
+            assert kw.get("wait") is False
+            submitted.append(1)
+            return _real(*a, **kw)
+
+        it.loader.copy_files_to_device = spy
+        gen = it.iterate_weights()
+        next(gen)                                  # the first tensor of the first batch
+        assert len(submitted) == 1 + ahead, queue_size
+        gen.close()
+        it.close()
+
+
+@pytest.mark.parametrize("producer_thread", [False, True], ids=["native_read_ahead", "producer_thread"])
+def test_consumer_may_stop_early(producer_thread, case_files, leak_check):
     paths = sorted(case_files(CASE))
-    it = fst.ParallelLoader(None, paths, queue_size=2, use_tqdm_on_load=False, device="cpu", nogds=True)
+    it = fst.ParallelLoader(None, paths, queue_size=2, use_tqdm_on_load=False, device="cpu", nogds=True,
+                            producer_thread=producer_thread)
     gen = it.iterate_weights()
     next(gen)
     gen.close()            # runs the generator's cleanup: producer stops, queued batches are freed
@@ -83,15 +115,15 @@ def test_only_one_producer_is_supported(case_files):
 
 def _rank_main(rank, world, paths, port, out_dir, queue_size, backend="gloo"):
     sys.path.insert(0, ROOT)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    rdzv = rendezvous(out_dir, port)
     device = "cpu"
     if backend == "nccl":
         torch.cuda.set_device(rank)
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         device = f"cuda:{rank}"
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(device))
+        dist.init_process_group("nccl", init_method=rdzv, rank=rank, world_size=world, device_id=torch.device(device))
     else:
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        dist.init_process_group("gloo", init_method=rdzv, rank=rank, world_size=world)
     it = fst.ParallelLoader(dist.group.WORLD, paths, queue_size=queue_size, use_tqdm_on_load=False,
                             device=device, nogds=True, max_threads=2, slot_kb=64)
     got = {}

@@ -10,7 +10,7 @@ import sys
 import pytest
 import torch.distributed as dist
 import torch.multiprocessing as mp
-from tests.helpers import free_port
+from tests.helpers import free_port, rendezvous
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -64,8 +64,8 @@ def _rank(rank, world, port, fail, out_dir):
     from fastsafetensors_b200 import batch
     from fastsafetensors_b200.st_types import Device
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    rdzv = rendezvous(out_dir, port)
+    dist.init_process_group("gloo", init_method=rdzv, rank=rank, world_size=world)
 
     class PG:
         real_pg = dist.group.WORLD

@@ -170,7 +170,8 @@ class Workload:
     layers, ``--files F`` to the tensors of its first F files (file boundaries stay those of the
     whole checkpoint)."""
 
-    def __init__(self, args, world: int):
+    def __init__(self, args, world: int, n_files: int = 0):
+        """``n_files`` > 0: the file count another rank has decided on (see ``_fit_to_disk``)."""
         import re
 
         from tests import synth
@@ -186,21 +187,56 @@ class Workload:
         self.spec = spec
         self.groups = synth.partition(spec)
         self.total_files = len(self.groups)
-        n_files = args.files or (8 if name == "llama3-70b" and args.scale == "full" else self.total_files)
-        self.n_files = max(1, min(n_files, self.total_files))
+        self.dir = os.path.join(args.dir, spec.name)
+        self.disk_note = ""
+        if n_files > 0:
+            self.n_files = n_files
+        else:
+            want = args.files or (8 if name == "llama3-70b" and args.scale == "full" else self.total_files)
+            self.n_files = max(1, min(want, self.total_files))
+            self.disk_note = self._fit_to_disk(args.dir, world)
         self.tp = spec.tp if world == 1 else world
         self.indices = [i for g in self.groups[: self.n_files] for i in g]   # tensor indices in the kept files
         self.tensors = [spec.tensors[i] for i in self.indices]
         self.data_bytes = sum(t.nbytes for t in self.tensors)
         full = plan_for(spec, self.tp)
         self.plan = OrderedDict((t.name, full[t.name]) for t in self.tensors)
-        self.dir = os.path.join(args.dir, spec.name)
         self.paths = sorted(os.path.join(self.dir, synth.file_name(spec, k, self.total_files))
                             for k in range(self.n_files))
         subset = "" if self.n_files == self.total_files else \
             f" (first {self.n_files} of its {self.total_files} files)"
         self.label = (f"{spec.name} ({args.scale}){subset}: {len(self.tensors)} tensors, "
                       f"{self.n_files} files, {self.data_bytes} data bytes, tensor-parallel {self.tp}-way")
+
+    def _fit_to_disk(self, top: str, world: int) -> str:
+        """Make sure the files that still have to be written fit the disk: remove this
+        benchmark's other checkpoints first, then keep fewer files (never fewer than one per
+        rank).  Returns a note for the log, empty if nothing had to be done."""
+        import shutil
+
+        from tests import synth
+
+        def missing_bytes(n_files: int) -> int:
+            need = 0
+            for k in range(n_files):
+                size = sum(self.spec.tensors[i].nbytes for i in self.groups[k]) + (1 << 20)
+                path = os.path.join(self.dir, synth.file_name(self.spec, k, self.total_files))
+                if not (os.path.exists(path) and os.path.getsize(path) >= size - (1 << 20)):
+                    need += size
+            return need
+
+        os.makedirs(top, exist_ok=True)
+        margin = 2 << 30
+        note = ""
+        if missing_bytes(self.n_files) + margin > shutil.disk_usage(top).free:
+            for other in sorted(os.listdir(top)):
+                if other != self.spec.name and os.path.isdir(os.path.join(top, other)):
+                    shutil.rmtree(os.path.join(top, other), ignore_errors=True)
+                    note += f"removed {other}; "
+        while self.n_files > max(1, world) and missing_bytes(self.n_files) + margin > shutil.disk_usage(top).free:
+            self.n_files -= 1
+            note += f"cut to {self.n_files} files (disk); "
+        return note
 
     def config_block(self) -> dict:
         """The ``config`` object: identical in both arms."""
@@ -213,7 +249,8 @@ class Workload:
         if rank == 0:
             t0 = time.time()
             synth.write_checkpoint(self.spec, self.dir, fsync=True, only_files=range(self.n_files))
-            sys.stderr.write(f"[bench] checkpoint {self.label} in {self.dir} ({time.time() - t0:.1f} s)\n")
+            sys.stderr.write(f"[bench] checkpoint {self.label} in {self.dir} ({time.time() - t0:.1f} s) "
+                             f"{self.disk_note}\n")
         barrier()
 
     def e2e_steps(self, args) -> int:
@@ -355,7 +392,11 @@ def b200_arm(args) -> dict:
     if args.other_kernels_only:
         return {"other_kernels": other_kernels(device, peak)} if rank == 0 else {}
 
-    wl = Workload(args, world)
+    # rank 0 looks at the disk and decides how many files the run keeps; the others follow
+    decided = [Workload(args, world).n_files if rank == 0 else 0]
+    if world > 1:
+        dist.broadcast_object_list(decided, src=0)
+    wl = Workload(args, world, n_files=decided[0])
     tp, plan, paths, data_bytes = wl.tp, wl.plan, wl.paths, wl.data_bytes
     wl.write(rank, barrier)
     owners = synth.owners(paths, world)

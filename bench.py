@@ -558,7 +558,9 @@ def b200_arm(args) -> dict:
                                                 "frac": round(target_ms / kernel_ms, 4) if kernel_ms else None}
 
     # ---------------------------------------------------------------- end to end (public API)
-    def e2e_step():
+    e2e_parity = {}
+
+    def e2e_step(check: bool = False):
         torch.cuda.synchronize()
         barrier()
         t0 = time.perf_counter()
@@ -578,6 +580,14 @@ def b200_arm(args) -> dict:
         t3 = time.perf_counter()
         barrier()
         t4 = time.perf_counter()
+        if check:        # outside the timed region: the shards this step produced, against regenerated data
+            if world == 1:
+                p = check_parity(wl, lambda n, d: (got[d][n].get_raw() if n in got[d] else None), range(tp))
+            else:
+                p = check_parity(wl, lambda n, d: (got[n].get_raw() if n in got else None), [rank])
+            every = all_ranks(p)
+            e2e_parity.update({"checked": sum(q["checked"] for q in every), "ok": all(q["ok"] for q in every),
+                               "mismatches": [m for q in every for m in q["mismatches"]][:5]})
         del got, probe
         buf.close()
         ld.close()
@@ -606,7 +616,7 @@ def b200_arm(args) -> dict:
                 barrier()
             if i == warmup_steps:
                 r0 = cpp.get_cpp_metrics().read_ns
-            dt, d2h, part = e2e_step()
+            dt, d2h, part = e2e_step(check=(not cold and i == warmup_steps + steps - 1))
             if i >= warmup_steps:
                 times.append(dt)
                 parts.append(part)
@@ -656,6 +666,13 @@ def b200_arm(args) -> dict:
         mD = cpp.get_cpp_metrics()
         result["e2e_warm"]["io"] = {"direct_requests": mD.direct_io_requests - mC.direct_io_requests,
                                     "buffered_requests": mD.buffered_io_requests - mC.buffered_io_requests}
+        # the shards of the last end-to-end step were checked too (files -> deferred reads ->
+        # pipelined pack and exchange), not only those of the resident phase
+        parity["e2e_checked"] = e2e_parity.get("checked", 0)
+        parity["checked"] += e2e_parity.get("checked", 0)
+        if not e2e_parity.get("ok", True):
+            parity["ok"] = False
+            parity["mismatches"] = (parity["mismatches"] + ["e2e: " + m for m in e2e_parity["mismatches"]])[:5]
     if not parity["ok"]:
         note(f"PARITY FAILURE: {parity['mismatches']}")
     # ---------------------------------------------------------------- upstream's CUDA path, same N

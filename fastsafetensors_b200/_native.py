@@ -45,7 +45,7 @@ EXPORTS = (
     "fst_realign", "fst_release_workspaces", "fst_arena_create", "fst_arena_export",
     "fst_arena_open_peer", "fst_arena_close_peer", "fst_arena_destroy", "fst_convert",
     "fst_cufile_available", "fst_gds_supported", "fst_reader_order_after", "fst_device_alloc",
-    "fst_device_free", "fst_memcpy_h2d_async",
+    "fst_device_free", "fst_memcpy_h2d_async", "fst_gather_limited",
 )
 
 
@@ -150,6 +150,7 @@ def _load() -> ctypes.CDLL:
         POINTER(Copy2D), c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64,
     ]
     lib.fst_gather_static.argtypes = lib.fst_gather.argtypes
+    lib.fst_gather_limited.argtypes = lib.fst_gather.argtypes + [ctypes.c_uint32]
     lib.fst_gather_host.argtypes = [POINTER(Copy2D), c_uint64, c_int]
     lib.fst_realign.argtypes = [c_uint64, c_uint64, c_uint64, c_uint64]
     lib.fst_release_workspaces.restype = c_int
@@ -228,6 +229,19 @@ def gather(ops: Sequence[Tuple[int, int, int, int, int, int]], stream: int,
     check(
         lib.fst_gather(arr, len(ops), src_span[0], src_span[1], dst_span[0], dst_span[1], stream),
         "fst_gather",
+    )
+
+
+def gather_limited(ops: Sequence[Tuple[int, int, int, int, int, int]], stream: int, max_ctas: int,
+                   src_span: Tuple[int, int] = (0, 0), dst_span: Tuple[int, int] = (0, 0)) -> None:
+    """``fst_gather_limited``: the device gather on a grid of at most ``max_ctas`` CTAs."""
+    if not ops:
+        return
+    arr = make_ops(ops)
+    check(
+        lib.fst_gather_limited(arr, len(ops), src_span[0], src_span[1], dst_span[0], dst_span[1], stream,
+                               max_ctas),
+        "fst_gather_limited",
     )
 
 

@@ -366,6 +366,15 @@ class ShardExchange:
         return per_dst
 
 
+def peer_remote_ctas(world: int) -> int:
+    """Grid bound of the launch that stores into the peers' arenas when this rank's own region
+    is packed by a second launch beside it (``FST_B200_PEER_REMOTE_CTAS``; 0 = one launch does
+    both, region after region)."""
+    import os
+
+    return max(0, int(os.environ.get("FST_B200_PEER_REMOTE_CTAS", "0")))
+
+
 def default_chunk_bytes() -> int:
     """Outgoing bytes per owner and chunk of a multi-rank exchange (``FST_B200_EXCHANGE_CHUNK_MB``,
     default 1024): small enough that the gather of one chunk hides under the transfer of the
@@ -588,6 +597,8 @@ class PeerShardExchange:
         self.egress_bytes = sum(ch.layout.region_bytes[me][d] for ch in self.chunks
                                 for d in range(world) if d != me)
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device.as_str())
+        self._side = None
+        self.remote_ctas = peer_remote_ctas(world)
 
     def _prepare(self, index: int) -> _Chunk:
         ch = self.chunks[index]
@@ -611,7 +622,15 @@ class PeerShardExchange:
         mine = {n: self.frames[n] for n in src_addr}
         ops = lay.fill_ops(me, mine, src_addr, region, rotate=True) if mine else []
         ch.payload = sum(o[2] * o[3] for o in ops)
-        ch.launches = [(nat.pack_ops(ops), len(ops))] if ops else []
+        lo, hi = self.arena.address, self.arena.address + self.arena.nbytes
+        own = [o for o in ops if lo <= o[1] < hi]
+        remote = [o for o in ops if not (lo <= o[1] < hi)]
+        if self.remote_ctas > 0 and own and remote:
+            # two launches side by side: the peer stores on a grid small enough to leave most of
+            # the SMs to this rank's own region (see run)
+            ch.launches = [(nat.pack_ops(remote), len(remote), "remote"), (nat.pack_ops(own), len(own), "own")]
+        else:
+            ch.launches = [(nat.pack_ops(ops), len(ops), "all")] if ops else []
         return ch
 
     def run(self, timing: Optional[list] = None, after_chunk=None) -> None:
@@ -620,19 +639,29 @@ class PeerShardExchange:
 
         from . import _native as nat
 
-        stream = self.fb.framework.current_stream(self.device)
+        cur = torch.cuda.current_stream()
         payload = 0
         for index in range(len(self.chunks)):
             ch = self._prepare(index)
             payload += ch.payload
-            for packed, n in ch.launches:
+            split = len(ch.launches) == 2
+            if split:
+                if self._side is None:
+                    self._side = torch.cuda.Stream()
+                self._side.wait_stream(cur)          # the images are ready on the caller's stream
+            for packed, n, kind in ch.launches:
+                stream = self._side if kind == "own" and split else cur
                 if timing is not None:
                     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record()
-                nat.check(nat.lib.fst_gather(packed.pointer, n, 0, 0, 0, 0, stream), "fst_gather")
+                    a.record(stream)
+                nat.check(nat.lib.fst_gather_limited(packed.pointer, n, 0, 0, 0, 0, int(stream.cuda_stream),
+                                                     self.remote_ctas if kind == "remote" else 0),
+                          "fst_gather")
                 if timing is not None:
-                    b.record()
+                    b.record(stream)
                     timing.append((a, b))
+            if split:
+                cur.wait_stream(self._side)          # before the image is released or reused
             if after_chunk is not None:
                 after_chunk(ch.names)
         self.payload_bytes = payload

@@ -578,6 +578,12 @@ extern "C" int fst_realign(uint64_t dst, uint64_t src, uint64_t nbytes, uint64_t
 extern "C" int fst_gather(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_base,
                           uint64_t src_len, uint64_t dst_base, uint64_t dst_len,
                           uint64_t stream) {
+    return fst_gather_limited(ops, n_ops, src_base, src_len, dst_base, dst_len, stream, 0);
+}
+
+extern "C" int fst_gather_limited(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_base,
+                                  uint64_t src_len, uint64_t dst_base, uint64_t dst_len,
+                                  uint64_t stream, uint32_t max_ctas) {
     using namespace fst;
     clear_error();
     if (!cuda_usable()) {
@@ -606,7 +612,8 @@ extern "C" int fst_gather(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_
     }
     cudaStream_t st = (cudaStream_t)stream;
     std::lock_guard<std::mutex> lock(g_ws_mutex);
-    const int limit = grid_limit_for(dev);
+    int limit = grid_limit_for(dev);
+    if (max_ctas > 0 && (int)max_ctas < limit) limit = (int)max_ctas;
 
     size_t pos = 0;
     while (pos < recs.size()) {

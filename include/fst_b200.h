@@ -227,6 +227,14 @@ typedef struct fst_copy2d {
 int fst_gather(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_base, uint64_t src_len,
                uint64_t dst_base, uint64_t dst_len, uint64_t stream);
 
+/* fst_gather with an upper bound on the number of CTAs of each launch (0 = the library's own
+ * rule).  The kernel strides over its work, so a small grid only means that each CTA takes more
+ * steps.  For copies whose destination is another GPU's memory: a few hundred CTAs keep enough
+ * stores in flight to fill NVLink, and leave the rest of the SMs to a second gather (this GPU's
+ * own region) running beside it on another stream.  (No counterpart in upstream.) */
+int fst_gather_limited(const fst_copy2d_t *ops, uint64_t n_ops, uint64_t src_base, uint64_t src_len,
+                       uint64_t dst_base, uint64_t dst_len, uint64_t stream, uint32_t max_ctas);
+
 /* fst_gather for callers that must not allocate.  (No counterpart in upstream: its native
  * layer has no kernels and therefore no kernel workspace.)
  *

@@ -59,3 +59,42 @@ def test_both_arms_describe_the_same_workload():
     assert sub.data_bytes == sum(t.nbytes for t in sub.tensors) < eight.data_bytes
     assert set(sub.plan) == {t.name for t in sub.tensors}
     assert 2 <= sub.e2e_steps(args) <= 20
+
+
+def test_bench_parity_expectation_agrees_with_the_oracle():
+    """The bench's in-run parity check regenerates tensor bytes and slices them with plain numpy;
+    here that slicing is held against the oracle's restatement of upstream's shard rule, and the
+    checker is shown to notice a wrong byte."""
+    sys.path.insert(0, ROOT)
+    import argparse
+
+    import numpy as np
+    import torch
+
+    import bench
+    from oracle import st_oracle
+    from tests import synth
+
+    args = argparse.Namespace(config="llama3-8b", scale="tiny", layers=0, files=0, dir="/tmp/x", steps=5, e2e_steps=0)
+    wl = bench.Workload(args, 8)
+    seen = set()
+    results = {}
+    for pos in bench.parity_sample(wl):
+        t = wl.tensors[pos]
+        action = wl.plan[t.name]
+        raw = synth.expected_bytes(wl.spec, wl.indices[pos])
+        for dst in range(wl.tp):
+            got = bench.expected_shard(t, raw, action, dst, wl.tp)
+            dim = action[1] if action[0] == "shard" else -1
+            want, _ = st_oracle.shard(raw, list(t.shape), t.dtype, dim, dst, wl.tp)
+            assert np.array_equal(got, want), (t.name, dst)
+            results[(t.name, dst)] = torch.from_numpy(np.array(got))
+        seen.add(action[0] + (str(action[1]) if action[0] == "shard" else ""))
+    assert seen == {"shard0", "shard1", "replicate"}
+    ok = bench.check_parity(wl, lambda n, d: results.get((n, d)), range(wl.tp))
+    assert ok["ok"] and ok["checked"] == len(results) and ok["kinds"] == ["replicate", "shard0", "shard1"]
+    name, dst = next(iter(results))
+    results[(name, dst)] = results[(name, dst)].clone()
+    results[(name, dst)][0] ^= 1
+    bad = bench.check_parity(wl, lambda n, d: results.get((n, d)), range(wl.tp))
+    assert not bad["ok"] and name in bad["mismatches"][0]

@@ -169,6 +169,33 @@ def test_owner_packing_for_all_ranks_matches_upstream(case, golden, case_files, 
     loader.close()
 
 
+@pytest.mark.parametrize("case", MULTI, ids=[c["id"] for c in MULTI])
+def test_shard_locally_with_deferred_reads_matches_upstream(case, golden, case_files, leak_check):
+    """The end-to-end call sequence of the benchmark on one GPU: reads queued without waiting,
+    ``shard_locally`` working through the files in read order, one gather launch per file; every
+    destination's tensors must be what upstream delivered to that rank."""
+    if case["steps"][0][0] != "plan":
+        pytest.skip("case has no whole-checkpoint plan")
+    paths = sorted(case_files(case))
+    world = case["world"]
+    plan = OrderedDict((n, (a[0], a[1] % world) if a[0] == "push" else a) for n, a in cases.plan(case))
+    before = cpp.get_cpp_metrics()
+    loader = fst.SafeTensorsFileLoader(fst.SingleGroup(), DEV, nogds=True, max_threads=4, slot_kb=64)
+    loader.add_filenames({0: paths})
+    fb = loader.copy_files_to_device(wait=False)
+    assert all(f.pending for f in fb.rank_loaders[0])
+    per_rank = fb.shard_locally(plan, world)
+    assert not any(f.pending for f in fb.rank_loaders[0])
+    launches = cpp.get_cpp_metrics().kernel_launches - before.kernel_launches
+    for rank, tensors in enumerate(per_rank):
+        want = {k: v for k, v in golden["cases"][case["id"]][rank].items() if v is not None}
+        assert {k: record(v) for k, v in tensors.items()} == want, rank
+    assert launches >= len(paths)          # at least one gather launch per file
+    del per_rank, tensors
+    fb.close()
+    loader.close()
+
+
 @pytest.mark.parametrize("shape,dim,world", [
     ((4096, 14336), 1, 8),     # Llama-3-8B down_proj
     ((14336, 4096), 0, 8),     # Llama-3-8B gate/up

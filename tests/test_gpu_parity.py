@@ -109,6 +109,21 @@ def test_gather_many_ops_inline_and_table_paths(n_ops):
     assert np.array_equal(got, expected_ops(src_np, 0, d_size, 0, ops))
 
 
+@pytest.mark.parametrize("max_ctas", [1, 7, 148])
+def test_gather_on_a_bounded_grid(max_ctas):
+    """fst_gather_limited: a few CTAs stride over all the work (inline and table paths)."""
+    for n_ops in (5, 300):
+        rng = np.random.default_rng(max_ctas * 1000 + n_ops)
+        ops, s_size, d_size = _random_ops(rng, n_ops, 6, 5000)
+        src_np = rng.integers(0, 256, s_size, dtype=np.uint8)
+        src = dev_bytes(src_np)
+        dst = torch.full((d_size,), CANARY, dtype=torch.uint8, device=DEV)
+        abs_ops = [(src.data_ptr() + o[0], dst.data_ptr() + o[1]) + tuple(o[2:]) for o in ops]
+        nat.gather_limited(abs_ops, stream(), max_ctas, (src.data_ptr(), src.numel()), (dst.data_ptr(), dst.numel()))
+        torch.cuda.synchronize()
+        assert np.array_equal(dst.cpu().numpy(), expected_ops(src_np, 0, d_size, 0, ops)), n_ops
+
+
 def test_gather_refuses_out_of_range_ops():
     src = torch.zeros(4096, dtype=torch.uint8, device=DEV)
     dst = torch.zeros(4096, dtype=torch.uint8, device=DEV)

@@ -114,20 +114,45 @@ class BatchLayout:
         slow remote stores hold up the local ones.)"""
         ops: List[shard_plan.Op] = []
         w = self.world
+
+        def op_for(slot: Slot, dst: int) -> shard_plan.Op:
+            frame = frames[slot.name]
+            _, action = self.where[slot.name]
+            to = region_addr[dst] + slot.offset
+            if action[0] == "shard":
+                lo, hi = shard_plan.shard_bounds(frame.shape[action[1]], w, dst)
+                return shard_plan.shard_op(src_addr[slot.name], to, frame.shape, frame.dtype.bits, action[1], lo, hi)
+            return (src_addr[slot.name], to, 1, slot.nbytes, 0, 0)
+
+        if rotate == "interleave":
+            # the owner's own region first, then tensor by tensor: the slots of one tensor in all
+            # the other destinations, starting with the next rank.  Every owner then stores to all
+            # its peers at once, so each rank's NVLink ingress is shared evenly whatever the
+            # owners' relative progress.
+            for slot in self.slots[me][me]:
+                if slot.nbytes:
+                    ops.append(op_for(slot, me))
+            by_name: List[Dict[str, Slot]] = [{s.name: s for s in self.slots[me][d]} for d in range(w)]
+            order: List[str] = []
+            seen = set()
+            for d in range(w):
+                for s in self.slots[me][d]:
+                    if s.name not in seen:
+                        seen.add(s.name)
+                        order.append(s.name)
+            for name in order:
+                for k in range(1, w):
+                    dst = (me + k) % w
+                    slot = by_name[dst].get(name)
+                    if slot is not None and slot.nbytes:
+                        ops.append(op_for(slot, dst))
+            return ops
         for k in range(w):
             dst = (me + k) % w if rotate else k
             for slot in self.slots[me][dst]:
                 if slot.nbytes == 0:
                     continue
-                frame = frames[slot.name]
-                _, action = self.where[slot.name]
-                to = region_addr[dst] + slot.offset
-                if action[0] == "shard":
-                    lo, hi = shard_plan.shard_bounds(frame.shape[action[1]], w, dst)
-                    ops.append(shard_plan.shard_op(src_addr[slot.name], to, frame.shape,
-                                                   frame.dtype.bits, action[1], lo, hi))
-                else:
-                    ops.append((src_addr[slot.name], to, 1, slot.nbytes, 0, 0))
+                ops.append(op_for(slot, dst))
         return ops
 
     def received(self, me: int) -> List[Tuple[Slot, int]]:
@@ -384,12 +409,15 @@ def peer_remote_ctas(world: int, device_index: int = 0) -> int:
 
 
 def default_chunk_bytes() -> int:
-    """Outgoing bytes per owner and chunk of a multi-rank exchange (``FST_B200_EXCHANGE_CHUNK_MB``,
-    default 1024): small enough that the gather of one chunk hides under the transfer of the
-    previous one, large enough that the collective's start-up cost does not show."""
+    """Outgoing bytes per owner and chunk of an exchange over NCCL.  Default: no cut below a
+    round (one file per owner).  ``FST_B200_EXCHANGE_CHUNK_MB`` cuts rounds further; on B200 that
+    measured slower, not faster (1 GiB chunks: 31 ms against 16 ms per step at two ranks, 48 ms at
+    four): the gather launches of the next chunk fill every SM and NCCL's copy kernels, which
+    need a few of them, queue behind."""
     import os
 
-    return max(1, int(os.environ.get("FST_B200_EXCHANGE_CHUNK_MB", "1024"))) << 20
+    env = os.environ.get("FST_B200_EXCHANGE_CHUNK_MB")
+    return (max(1, int(env)) << 20) if env else (1 << 62)
 
 
 class PeerArenaUnavailable(RuntimeError):
@@ -574,7 +602,10 @@ class PeerShardExchange:
     """
 
     def __init__(self, fb, requests: "Dict[str, Action]", world: int, me: int,
-                 chunk_bytes: Optional[int] = None):
+                 chunk_bytes: Optional[int] = None, arena=None):
+        """``arena``: an object with ``address``, ``nbytes``, ``peer_base`` and ``view`` to use
+        instead of creating a ``PeerArena`` (several ranks emulated by one process on one GPU;
+        the closing all-reduce is then left to the caller)."""
         import torch
 
         self.fb, self.world, self.me, self.local = fb, world, me, False
@@ -598,7 +629,9 @@ class PeerShardExchange:
             for r in range(world):
                 total[r] += lay.recv_total(r)
         # every rank allocates for the neediest rank, so that all decide alike
-        self.arena = PeerArena.for_group(fb.pg, max(total), self.device)
+        self.recv_need = max(total)
+        self._own_arena = arena is None
+        self.arena = PeerArena.for_group(fb.pg, max(total), self.device) if arena is None else arena
         self.recv = self.arena.view(total[me])
         self.send = None
         self.payload_bytes = 0
@@ -607,6 +640,11 @@ class PeerShardExchange:
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device.as_str())
         self._side = None
         self.remote_ctas = peer_remote_ctas(world, self.device.index or 0)
+        import os
+
+        # order of the peer stores: "region" = one destination after the other, rotated per
+        # owner; "interleave" = tensor by tensor to all destinations (see BatchLayout.fill_ops)
+        self.order = "interleave" if os.environ.get("FST_B200_PEER_ORDER", "region") == "interleave" else True
 
     def _prepare(self, index: int) -> _Chunk:
         ch = self.chunks[index]
@@ -628,7 +666,7 @@ class PeerShardExchange:
         base = self.chunk_base[index]
         region = [self.arena.peer_base[d] + base[d] + lay.recv_offset(d, me) for d in range(self.world)]
         mine = {n: self.frames[n] for n in src_addr}
-        ops = lay.fill_ops(me, mine, src_addr, region, rotate=True) if mine else []
+        ops = lay.fill_ops(me, mine, src_addr, region, rotate=self.order) if mine else []
         ch.payload = sum(o[2] * o[3] for o in ops)
         lo, hi = self.arena.address, self.arena.address + self.arena.nbytes
         own = [o for o in ops if lo <= o[1] < hi]
@@ -674,7 +712,8 @@ class PeerShardExchange:
                 after_chunk(ch.names)
         self.payload_bytes = payload
         # every rank's kernels are complete (a kernel's peer stores are visible when it completes)
-        dist.all_reduce(self._flag, group=self.fb.pg.real_pg)
+        if self._own_arena:
+            dist.all_reduce(self._flag, group=self.fb.pg.real_pg)
 
     def _view(self, slot: Slot, off: int):
         from .frameworks._torch import TorchTensor, dtype_convert
@@ -693,7 +732,8 @@ class PeerShardExchange:
 
     def close(self) -> None:
         """Collective: the peers let go of each other's arenas (the results stay valid)."""
-        self.arena.close_peers()
+        if self._own_arena:
+            self.arena.close_peers()
 
     def finish(self) -> None:
         self.close()

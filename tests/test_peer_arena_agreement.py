@@ -125,7 +125,8 @@ def test_transport_resolution(monkeypatch):
     cpu, gpu = Device.from_str("cpu"), Device.from_str("cuda:0")
     monkeypatch.delenv("FST_B200_TRANSPORT", raising=False)
     assert resolve_transport(None, 2, gpu) == "auto"
-    assert resolve_transport(None, 4, gpu) == "nccl"       # auto only where peer measured faster
+    assert resolve_transport(None, 8, gpu) == "auto"       # one NVSwitch machine: try peer, fall back
+    assert resolve_transport(None, 16, gpu) == "nccl"
     assert resolve_transport("peer", 8, gpu) == "peer"
     assert resolve_transport(None, 2, cpu) == "nccl"
     monkeypatch.setenv("FST_B200_TRANSPORT", "nccl")

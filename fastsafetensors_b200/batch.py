@@ -100,18 +100,18 @@ class BatchLayout:
         return sum(self.send_sizes(me)[:dst])
 
     def fill_ops(self, me: int, frames: Dict[str, TensorFrame], src_addr: Dict[str, int],
-                 region_addr: Sequence[int], rotate: bool = False) -> List[shard_plan.Op]:
+                 region_addr: Sequence[int], rotate=False) -> List[shard_plan.Op]:
         """Copies by which owner ``me`` fills its outgoing regions, region by region;
         ``region_addr[dst]`` is where region ``[me -> dst]`` starts (the send buffer, the receive
         buffer for ``dst == me``, or a peer's arena).
 
         ``rotate`` is for destinations that are peers' memories, where the order of the ops
-        matters because the gather kernel works through them in order: regions are then visited
-        starting with the owner's own and going round (me+1, me+2, ...), so that at any moment
-        different owners are storing to different ranks instead of all of them queueing on one
-        rank's NVLink ingress.  (Measured at N = 4: rotated, region by region 4.86 ms per launch;
-        tensor by tensor with local and remote stores interleaved 6.14 ms -- warps stalled on
-        slow remote stores hold up the local ones.)"""
+        matters because the gather kernel works through them in order.  ``True``: regions are
+        visited starting with the owner's own and going round (me+1, me+2, ...), so that at any
+        moment different owners are storing to different ranks instead of all of them queueing
+        on one rank's NVLink ingress.  ``"interleave"``: the own region first, then the peers'
+        regions tensor by tensor (measured at four ranks, peer stores in a launch of their own:
+        12.9 ms per step against 13.2 ms region by region)."""
         ops: List[shard_plan.Op] = []
         w = self.world
 
@@ -394,10 +394,12 @@ class ShardExchange:
 def peer_remote_ctas(world: int, device_index: int = 0) -> int:
     """Grid bound of the launch that stores into the peers' arenas while this rank's own region
     is packed by a second launch beside it; 0 = one launch does both, region after region.
-    ``FST_B200_PEER_REMOTE_CTAS`` sets it; the default is one CTA per SM, which measured best
-    on two B200 (13.9 ms per step against 16.6 ms with one launch, 14.9 with half and 15.7 with
-    twice as many CTAs): enough stores in flight to fill NVLink, and three quarters of the CTA
-    slots left to the own region."""
+    ``FST_B200_PEER_REMOTE_CTAS`` sets it.  The default is ``world // 2`` CTAs per SM (at most
+    four, the kernel's residency): enough stores in flight to fill NVLink towards ``world - 1``
+    peers, and CTA slots left to the own region.  Measured on B200, ms per step of a 38 GB
+    checkpoint -- two ranks: 16.6 with one launch, 14.9 / 13.9 / 15.7 / 15.4 with 74 / 148 / 296 /
+    592 CTAs; four ranks: 14.0 with one launch, 14.2 / 12.9 / 13.0 / 13.6 with 148 / 296 / 444 /
+    592 CTAs."""
     import os
 
     env = os.environ.get("FST_B200_PEER_REMOTE_CTAS")
@@ -405,7 +407,8 @@ def peer_remote_ctas(world: int, device_index: int = 0) -> int:
         return max(0, int(env))
     import torch
 
-    return int(torch.cuda.get_device_properties(device_index).multi_processor_count)
+    sms = int(torch.cuda.get_device_properties(device_index).multi_processor_count)
+    return sms * max(1, min(4, world // 2))
 
 
 def default_chunk_bytes() -> int:
@@ -644,7 +647,7 @@ class PeerShardExchange:
 
         # order of the peer stores: "region" = one destination after the other, rotated per
         # owner; "interleave" = tensor by tensor to all destinations (see BatchLayout.fill_ops)
-        self.order = "interleave" if os.environ.get("FST_B200_PEER_ORDER", "region") == "interleave" else True
+        self.order = "interleave" if os.environ.get("FST_B200_PEER_ORDER", "interleave") == "interleave" else True
 
     def _prepare(self, index: int) -> _Chunk:
         ch = self.chunks[index]

@@ -194,15 +194,6 @@ def get_metrics() -> Metrics:
     return m
 
 
-def make_ops(ops: Sequence[Tuple[int, int, int, int, int, int]]):
-    """Pack (src, dst, rows, row_bytes, src_pitch, dst_pitch) tuples into a C array."""
-    arr = (Copy2D * len(ops))()
-    for i, o in enumerate(ops):
-        a = arr[i]
-        a.src, a.dst, a.rows, a.row_bytes, a.src_pitch, a.dst_pitch = o
-    return arr
-
-
 class PackedOps:
     """An op table packed once for repeated launches: a contiguous ``(n, 6)`` uint64 array
     (one ``fst_copy2d_t`` per row, filled without a Python loop per field) and the pointer the
@@ -218,6 +209,15 @@ class PackedOps:
 
 def pack_ops(ops: Sequence[Tuple[int, int, int, int, int, int]]) -> PackedOps:
     return PackedOps(ops)
+
+
+def make_ops(ops: Sequence[Tuple[int, int, int, int, int, int]]):
+    """Pack (src, dst, rows, row_bytes, src_pitch, dst_pitch) tuples; returns the pointer the C
+    entry points take (it keeps its array alive)."""
+    packed = PackedOps(ops)
+    pointer = packed.pointer
+    pointer._fst_keepalive = packed
+    return pointer
 
 
 def gather(ops: Sequence[Tuple[int, int, int, int, int, int]], stream: int,

@@ -1,5 +1,5 @@
 """Batched redistribution plan: many tensors, all destination ranks, one gather launch per file
-and one exchange per batch.
+and chunk, transfers overlapped with the reads of the files still to come.
 
 Upstream moves one tensor per collective (``tensor_factory.py:143,186,258``: a broadcast or a
 scatter per tensor, each followed by a device-wide synchronisation).  With file ownership dealt
@@ -13,9 +13,12 @@ exchange out explicitly:
 * the owner fills its ``W`` outgoing regions with one gather launch per chunk
   (``fill_ops``: shards as strided copies, replicated and pushed tensors as flat copies), writing
   its own region straight into the receive buffer;
-* one ``all_to_all_single`` per chunk with the region sizes as split sizes moves the data while
-  the next chunk is being packed (and, with deferred reads, read); results are typed views of
-  the receive buffer.
+* ``ShardExchange``: one ``all_to_all_single`` per chunk (by default a chunk is a round: the
+  j-th file of every owner) with the region sizes as split sizes moves the data while the next
+  round is being packed (and, with deferred reads, read);
+* ``PeerShardExchange``: no collective moves data at all -- the gather launches store into the
+  destination ranks' memory over NVLink, and one small all-reduce closes the exchange;
+* results are typed views of one receive buffer.
 """
 
 from __future__ import annotations

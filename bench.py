@@ -83,7 +83,7 @@ def parse_args():
     ap.add_argument("--ref-settings", default="best", choices=("best", "defaults", "tuned"),
                     help="--impl reference: upstream's library defaults, the rule of its perf tool, or "
                          "whichever of the two is faster in one untimed step each")
-    ap.add_argument("--ref-budget", type=float, default=240.0,
+    ap.add_argument("--ref-budget", type=float, default=330.0,
                     help="--impl reference: seconds the resident phase may take before its steps are cut "
                          "to the first files of the checkpoint")
     ap.add_argument("--layers", type=int, default=0,

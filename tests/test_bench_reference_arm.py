@@ -98,3 +98,35 @@ def test_bench_parity_expectation_agrees_with_the_oracle():
     results[(name, dst)][0] ^= 1
     bad = bench.check_parity(wl, lambda n, d: results.get((n, d)), range(wl.tp))
     assert not bad["ok"] and name in bad["mismatches"][0]
+
+
+def test_workload_is_cut_to_what_the_disk_holds(tmp_path, monkeypatch):
+    """A checkpoint that does not fit the free disk space: other checkpoints of the benchmark
+    directory go first, then files are dropped from the end, never below one per rank."""
+    sys.path.insert(0, ROOT)
+    import argparse
+    import collections
+    import shutil
+
+    import bench
+
+    top = tmp_path / "bench"
+    (top / "some-older-checkpoint").mkdir(parents=True)
+    (top / "some-older-checkpoint" / "x.safetensors").write_bytes(b"0" * 10)
+    args = argparse.Namespace(config="llama3-70b", scale="tiny", layers=0, files=0, dir=str(top), steps=5,
+                              e2e_steps=0)
+    whole = bench.Workload(args, 8)
+    assert whole.n_files == 30 and whole.disk_note == ""
+    assert (top / "some-older-checkpoint").exists()
+    per_file = max(sum(whole.spec.tensors[i].nbytes for i in g) for g in whole.groups) + (1 << 20)
+    usage = collections.namedtuple("usage", "total used free")
+    room = 12                                                   # files that still fit
+    monkeypatch.setattr(shutil, "disk_usage", lambda p: usage(1 << 40, 0, (2 << 30) + room * per_file))
+    cut = bench.Workload(args, 8)
+    assert 8 <= cut.n_files < 30 and "cut to" in cut.disk_note and "removed some-older-checkpoint" in cut.disk_note
+    assert not (top / "some-older-checkpoint").exists()
+    assert len(cut.paths) == cut.n_files and f"first {cut.n_files} of its 30 files" in cut.label
+    monkeypatch.setattr(shutil, "disk_usage", lambda p: usage(1 << 40, 0, 1 << 30))
+    assert bench.Workload(args, 8).n_files == 8                  # one file per rank is the floor
+    # a file count decided elsewhere (rank 0) is taken as it is
+    assert bench.Workload(args, 8, n_files=11).n_files == 11

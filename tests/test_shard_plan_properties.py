@@ -62,3 +62,36 @@ def test_multi_col_ops_equal_numpy_concatenation(case):
         want, want_shape = st_oracle.multi_cols(raws, shapes, "F16", dim, r, world)
         assert shape == want_shape
         assert np.array_equal(packed[r * per_rank:(r + 1) * per_rank], want)
+
+
+def test_store_orders_of_an_owner_are_permutations_of_each_other():
+    """BatchLayout.fill_ops: region by region, rotated region by region, and tensor by tensor to
+    all destinations emit the same copies in different orders; the own region always comes first
+    in the two orders meant for peers' memory."""
+    from fastsafetensors_b200.batch import BatchLayout
+    from fastsafetensors_b200.common import TensorFrame
+    from fastsafetensors_b200.st_types import DType
+
+    world, me = 4, 2
+    lay = BatchLayout(world)
+    frames, src = {}, {}
+    specs = [("q", (8, 16), ("shard", 0)), ("o", (8, 16), ("shard", 1)), ("norm", (16,), ("replicate",)),
+             ("expert", (4, 4), ("push", 1)), ("mine", (4, 4), ("push", me)), ("empty", (0, 4), ("shard", 0))]
+    off = 0
+    for i, (name, shape, action) in enumerate(specs):
+        n = int(np.prod(shape)) * 2
+        frames[name] = TensorFrame.from_buffer({"dtype": "BF16", "shape": list(shape), "data_offsets": [off, off + n]})
+        src[name] = 0x10000 + off
+        off += n
+        lay.add(name, frames[name], me, action)
+    region = [0x1000000 * (d + 1) for d in range(world)]
+    plain = lay.fill_ops(me, frames, src, region)
+    rotated = lay.fill_ops(me, frames, src, region, rotate=True)
+    interleaved = lay.fill_ops(me, frames, src, region, rotate="interleave")
+    assert sorted(plain) == sorted(rotated) == sorted(interleaved) and len(plain) == len(set(plain))
+    own = [o for o in plain if region[me] <= o[1] < region[me] + 0x1000000]
+    assert rotated[: len(own)] == own and interleaved[: len(own)] == own
+    # tensor by tensor: the three peers' slots of "q" are adjacent, starting with rank me + 1
+    peers = interleaved[len(own):]
+    firsts = [(o[1] >> 24) - 1 for o in peers[:3]]
+    assert firsts == [(me + 1) % world, (me + 2) % world, (me + 3) % world]

@@ -114,6 +114,28 @@ static void failing_reads(const std::string &path, size_t size) {
     EXPECT(fst_reader_destroy(reader) == FST_OK);
 }
 
+// A wait that runs out of time leaves the request registered: polling with a zero timeout until
+// the request completes must end with FST_OK and the right bytes, and only then is the id
+// forgotten.  Ordering a host reader behind a stream is accepted and does nothing.
+static void polled_wait(const std::string &path, const std::vector<unsigned char> &want) {
+    const uint64_t reader = make_reader(1, FST_IO_DIRECT, 4096);
+    std::vector<unsigned char> dst(want.size());
+    EXPECT(fst_reader_order_after(reader, 0) == FST_OK);
+    int64_t id = 0;
+    uint64_t done = 0;
+    EXPECT(fst_reader_submit(reader, path.c_str(), 0, want.size(), (uint64_t)dst.data(), dst.size(), 0, &id) == FST_OK);
+    int rc = FST_ETIMEOUT;
+    long polls = 0;
+    while (rc == FST_ETIMEOUT && polls < 50000000) {
+        rc = fst_reader_wait(reader, id, 0, &done);
+        ++polls;
+    }
+    EXPECT(rc == FST_OK && done == want.size());
+    EXPECT(std::memcmp(dst.data(), want.data(), want.size()) == 0);
+    EXPECT(fst_reader_wait(reader, id, 0, &done) == FST_EINVAL);
+    EXPECT(fst_reader_destroy(reader) == FST_OK);
+}
+
 static void host_gather(int threads) {
     const uint64_t rows = 777, width = 3001, parts = 7;
     const std::vector<unsigned char> src = pattern(rows * width, 99);
@@ -150,7 +172,9 @@ int main(int argc, char **argv) {
     for (int i = 0; i < 6; ++i) callers.emplace_back(caller, std::cref(path), std::cref(data), i);
     std::thread gather_a(host_gather, 1), gather_b(host_gather, 5);
     std::thread failing(failing_reads, std::cref(path), data.size());
+    std::thread polling(polled_wait, std::cref(path), std::cref(data));
     for (auto &t : callers) t.join();
+    polling.join();
     gather_a.join();
     gather_b.join();
     failing.join();

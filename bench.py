@@ -699,24 +699,34 @@ def b200_arm(args) -> dict:
     return result if rank == 0 else {"parity_ok": parity["ok"]}
 
 
+KERNEL_SOURCE = os.path.join(ROOT, "fastsafetensors_b200", "csrc", "fst_kernels.cu")
+DEVICE_CODE_END = "// Host side: argument checks"
+
+
+def gather_device_code_hash() -> str:
+    """SHA-256 (16 hex digits) of the device code of the gather and realign kernels: the kernel
+    source file up to the comment that opens its host side."""
+    text = open(KERNEL_SOURCE, encoding="utf-8").read()
+    return hashlib.sha256(text[: text.index(DEVICE_CODE_END)].encode()).hexdigest()[:16]
+
+
 def recorded_traffic(alg_bytes_per_launch: float) -> dict:
     """DRAM traffic of a gather launch from the recorded profiler capture: the ratio of dram
     read+write bytes to algorithmic bytes measured on a small case of this kernel, kept in
-    ``profiles/fst_gather_kernel_traffic.json`` with a hash of the kernel source it was taken
-    from.  Traffic grows in proportion to the units processed, so the ratio scales to a full
-    launch.  If the source has changed since the capture the figure is marked as a constant."""
+    ``profiles/fst_gather_kernel_traffic.json`` with a hash of the kernel's device code.  Traffic
+    grows in proportion to the units processed, so the ratio scales to a full launch.  If the
+    device code has changed since the capture the figure is marked as a constant."""
     path = os.path.join(ROOT, "profiles", "fst_gather_kernel_traffic.json")
     try:
         rec = json.load(open(path))
-        src = os.path.join(ROOT, "fastsafetensors_b200", "csrc", "fst_kernels.cu")
-        current = hashlib.sha256(open(src, "rb").read()).hexdigest()[:16]
+        current = gather_device_code_hash()
         ratio = float(rec["dram_bytes_per_algorithmic_byte"])
     except (OSError, ValueError, KeyError):
         return {"traffic": None, "traffic_source": "no recorded capture"}
-    fresh = current == rec.get("kernel_source_sha256_16")
+    fresh = current == rec.get("device_code_sha256_16")
     return {"traffic": int(ratio * alg_bytes_per_launch),
             "traffic_source": ("profiler capture of a small case x units processed"
-                               if fresh else "constant: the kernel source changed after the recorded capture"),
+                               if fresh else "constant: the kernel's device code changed after the recorded capture"),
             "traffic_ratio": ratio}
 
 

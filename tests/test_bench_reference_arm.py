@@ -130,3 +130,14 @@ def test_workload_is_cut_to_what_the_disk_holds(tmp_path, monkeypatch):
     assert bench.Workload(args, 8).n_files == 8                  # one file per rank is the floor
     # a file count decided elsewhere (rank 0) is taken as it is
     assert bench.Workload(args, 8, n_files=11).n_files == 11
+
+
+def test_recorded_traffic_ratio_belongs_to_the_current_kernel():
+    """The DRAM-traffic ratio the bench reports comes from a profiler capture; it is only
+    presented as such while the gather kernel's device code is the code that was captured."""
+    sys.path.insert(0, ROOT)
+    import bench
+
+    rec = bench.recorded_traffic(2.0e9)
+    assert rec["traffic_source"].startswith("profiler capture"), rec
+    assert 0.9 < rec["traffic_ratio"] <= 1.05 and rec["traffic"] == int(rec["traffic_ratio"] * 2.0e9)
